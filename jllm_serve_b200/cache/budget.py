@@ -31,9 +31,10 @@ class PagePlan:
         return self.pages * self.bytes_per_page
 
 
-def group_page_bytes(runs: int, kv_heads: int, head_dim: int, page_size: int, element_bytes: int) -> int:
-    """Bytes of one page of a group: keys and values of `page_size` positions for each of its layer runs."""
-    return runs * 2 * kv_heads * page_size * head_dim * element_bytes
+def group_page_bytes(runs: int, kv_heads: int, head_dim: int, page_size: int, element_bytes: int, planes: int = 2) -> int:
+    """Bytes of one page of a group: keys and values (`planes` = 2; 1 where one row serves as both) of `page_size`
+    positions for each of its layer runs."""
+    return runs * planes * kv_heads * page_size * head_dim * element_bytes
 
 
 def plan_pages(free_bytes: int, total_bytes: int, page_bytes_by_group: Sequence[int], page_size: int, ctx: int,

@@ -45,6 +45,8 @@ class PagedKeysValues(CacheNeed):
     kv_heads: int
     head_dim: int
     window: int = 0                        # 0 = every earlier position, else the last `window`
+    planes: int = 2                        # 2: keys and values; 1: one row per position that serves as both (a latent
+                                           # from which a mixer makes its keys and values)
 
 
 @dataclass(frozen=True)
@@ -58,12 +60,13 @@ class PagedGroup:
     need: PagedKeysValues
     runs: List[int]                        # schedule indices of the member layer runs
     pool: Optional[PoolView] = None        # a view of the group's page pool
-    storage: object = None                 # [len(runs), 2, pages, kv_heads, page_size, head_dim]
+    storage: object = None                 # [len(runs), planes, pages, kv_heads, page_size, head_dim]
 
     def keys_values(self, run: int):
-        """(K, V) of one member run: each [pages, kv_heads, page_size, head_dim]."""
+        """(K, V) of one member run: each [pages, kv_heads, page_size, head_dim]; the same rows twice in a group of
+        one plane."""
         i = self.runs.index(run)
-        return self.storage[i, 0], self.storage[i, 1]
+        return self.storage[i, 0], self.storage[i, self.need.planes - 1]
 
 
 @dataclass
@@ -191,7 +194,8 @@ class CacheManager:
         self._ints = (ctypes.c_int * max(8, G))()
         if allocate is not None:
             for g in self.paged:
-                g.storage = allocate((len(g.runs), 2, num_pages, g.need.kv_heads, page_size, g.need.head_dim), "kv")
+                g.storage = allocate((len(g.runs), g.need.planes, num_pages, g.need.kv_heads, page_size,
+                                      g.need.head_dim), "kv")
             for g in self.fixed:
                 g.storage = allocate((len(g.runs), max_requests) + tuple(g.need.shape), g.need.dtype)
 
@@ -238,8 +242,8 @@ class CacheManager:
     def page_bytes(needs: Sequence, page_size: int, element_bytes: int) -> List[int]:
         """Bytes of one page of every paged group these needs would form (for sizing the pool before it exists)."""
         from .budget import group_page_bytes
-        return [group_page_bytes(len(g.runs), g.need.kv_heads, g.need.head_dim, page_size, element_bytes)
-                for g in group_runs(needs)[0]]
+        return [group_page_bytes(len(g.runs), g.need.kv_heads, g.need.head_dim, page_size, element_bytes,
+                                 g.need.planes) for g in group_runs(needs)[0]]
 
     # ---- requests ---------------------------------------------------------------------------------------
     def open(self, request: Hashable) -> RequestCache:

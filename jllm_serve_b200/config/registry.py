@@ -47,14 +47,20 @@ def architecture_entry(model_type: str) -> ArchitectureEntry:
     return _ARCHITECTURES[model_type]
 
 
-def parse_config(values: dict):
-    """config.json as a dict -> the typed spec of its architecture."""
+def model_type_of(values: dict) -> str:
+    """The registry key of a config.json: `model_type`, or, in a config that has none, the name under `architecture`."""
     if not isinstance(values, dict):
         raise ConfigError("config.json must hold a JSON object")
-    model_type = values.get("model_type")
-    if not isinstance(model_type, str):
-        raise ConfigError("config.json: required key 'model_type' is missing")
-    return architecture_entry(model_type).parse(values)
+    for key in ("model_type", "architecture"):
+        name = values.get(key)
+        if isinstance(name, str):
+            return name
+    raise ConfigError("config.json: required key 'model_type' is missing")
+
+
+def parse_config(values: dict):
+    """config.json as a dict -> the typed spec of its architecture."""
+    return architecture_entry(model_type_of(values)).parse(values)
 
 
 def load_config(model_dir) -> tuple:

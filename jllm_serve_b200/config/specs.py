@@ -55,7 +55,7 @@ class RopeTableSpec:
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str = "rmsnorm"
+    kind: str = "rmsnorm"                  # rmsnorm | dynamic_tanh (tanh(a x) * w + b: no statistics, eps unused)
     eps: float = 1e-6
 
 
@@ -93,6 +93,51 @@ class GqaAttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class GatedLinearAttentionSpec(MixerSpec):
+    """Linear attention with a decay gate per key channel and a recurrent state [heads, key_dim, value_dim] per request:
+    S_t = diag(d_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, d_t = sigmoid(W2 (W1 h_t) + b2)^(1 / decay_temperature);
+    every head's o_t is RMS-normed (one gain of value_dim values for all heads), gated by silu(Wg h_t) and projected."""
+    kind: str = field(default="gated_linear_attention", init=False)
+    heads: int = 0
+    key_dim: int = 0                       # query and key channels per head
+    value_dim: int = 0                     # value channels per head
+    decay_rank: int = -1                   # width of the low-rank decay projection (rows of W1); -1: the checkpoint's own
+    decay_temperature: float = 1.0         # tau
+    norm_eps: float = 1e-6
+    query_scale: float = 0.0               # multiplier of q (key_dim^-1/2 in the designs seen so far)
+
+    def __post_init__(self):
+        for name in ("heads", "key_dim", "value_dim"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"gated linear attention: {name}={getattr(self, name)} must be positive")
+        if self.decay_rank == 0 or self.decay_rank < -1:
+            raise ConfigError(f"gated linear attention: decay_rank={self.decay_rank} must be positive (or -1: as stored)")
+        if not self.decay_temperature > 0:
+            raise ConfigError(f"gated linear attention: tau={self.decay_temperature} must be positive")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Causal softmax attention whose keys and values are two projections of one cached latent row per position
+    (c_t = rmsnorm(Wd h_t) * gain, k = Wuk c, v = Wuv c per head), without rotation, with a sigmoid gate per head on the
+    output (`gated`)."""
+    kind: str = field(default="latent_attention", init=False)
+    heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    rank: int = 0                          # width of the latent
+    scale: float = 0.0                     # multiplier of q . k
+    norm_eps: float = 1e-6
+    window: int = 0
+    gated: bool = True
+
+    def __post_init__(self):
+        for name in ("heads", "key_dim", "value_dim", "rank"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"latent attention: {name}={getattr(self, name)} must be positive")
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str = field(default="", init=False)
 
@@ -109,6 +154,29 @@ class DenseGluSpec(FeedForwardSpec):
             raise ConfigError(f"intermediate_size must be positive for a dense feed-forward, got {self.hidden}")
         if self.activation != "silu":
             raise ConfigError(f"unsupported hidden_act {self.activation!r}: only silu (SwiGLU) is built")
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec(FeedForwardSpec):
+    """`experts` gated feed-forwards of `hidden` units, of which a token uses `top`: scores s = sigmoid(Wr h); the `top`
+    largest of s + correction are chosen (if `correction`); the weights are the chosen s over their sum (+ 1e-20, if
+    `normalize`), times `scale`."""
+    kind: str = field(default="routed_experts", init=False)
+    experts: int = 0
+    top: int = 0
+    hidden: int = 0
+    scale: float = 1.0
+    correction: bool = True
+    normalize: bool = True
+    activation: str = "silu"
+
+    def __post_init__(self):
+        if self.experts <= 0 or self.hidden <= 0:
+            raise ConfigError(f"routed experts: experts={self.experts} and ff={self.hidden} must be positive")
+        if not 1 <= self.top <= self.experts:
+            raise ConfigError(f"routed experts: top={self.top} must lie in [1, experts={self.experts}]")
+        if self.activation != "silu":
+            raise ConfigError(f"unsupported expert activation {self.activation!r}: only silu is built")
 
 
 @dataclass(frozen=True)
@@ -131,12 +199,15 @@ class ModelNames:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a mixer, a feed-forward, the norm before each, and how they are arranged."""
+    """One layer: a mixer, a feed-forward (None: the layer has none, and no norm for it), the norm before each, and how
+    they are arranged."""
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     norm: NormSpec
-    arrangement: str = "pre_norm"          # x += mixer(norm(x)); x += ffn(norm(x))
+    arrangement: str = "pre_norm"          # x += s * mixer(norm(x)); x += s * ffn(norm(x)), s = residual_scale
     names: LayerNames = LayerNames()
+    residual_scale: float = 1.0
+    prefix: Optional[str] = None           # the layer's checkpoint prefix where it is not ModelNames.layer.format(index)
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,103 @@
+// Routed experts: the router, and the weighting of the experts' hidden rows.
+//
+// The router scores every expert for every row in float32: s = sigmoid(Wr h), Wr [experts, dim] float32. The `top`
+// experts with the largest s + correction are chosen (the lowest index wins a tie); the row's weights are the chosen s
+// divided by their sum + 1e-20 (if `normalize`), times `scale`; the others get 0. The weights leave as a dense
+// [rows, experts] float32 table: the feed-forward runs the experts as ONE product over their stacked gate / up rows
+// and ONE over their down matrices laid side by side along k, and a row's hidden values of expert e are multiplied by
+// its weight in between (`scale_expert_hidden`), so that experts a row does not use add exactly nothing.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, VecRef correction, int has_correction,
+                     float* __restrict__ weights, int dim, int experts, int top, float scale, int normalize) {
+    extern __shared__ float smem[];
+    float* s = smem;                   // [experts] scores
+    float* c = s + experts;            // [experts] choice scores, -inf once taken
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const T* row = h + (size_t)r * ld;
+    for (int e = warp; e < experts; e += warps) {
+        const float* wr = router + (size_t)e * dim;
+        float acc = 0.f;
+        for (int i = lane; i < dim; i += 32) acc = fmaf(to_float(row[i]), wr[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float sc = 1.f / (1.f + expf(-acc));
+            s[e] = sc;
+            c[e] = has_correction ? sc + correction[e] : sc;
+        }
+    }
+    __syncthreads();
+    float* out = weights + (size_t)r * experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) out[e] = 0.f;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = 0;
+            float bv = -INFINITY;
+            for (int e = 0; e < experts; ++e)
+                if (c[e] > bv) { bv = c[e]; best = e; }
+            c[best] = -INFINITY;
+            out[best] = s[best];
+            sum += s[best];
+        }
+        const float f = normalize ? scale / (sum + 1e-20f) : scale;
+        for (int e = 0; e < experts; ++e) out[e] = __fmul_rn(out[e], f);
+    }
+}
+
+template <typename T>
+__global__ void scale_expert_hidden_kernel(T* __restrict__ hidden, const float* __restrict__ weights, int experts, int ff,
+                                           size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t width = (size_t)experts * ff;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width, col = i - r * width;
+        hidden[i] = from_float<T>(__fmul_rn(to_float(hidden[i]), weights[r * experts + col / ff]));
+    }
+}
+
+}  // namespace
+
+// h [rows, ld] of type `dtype` (the normed rows); router [experts, dim] float32; correction [experts] or null;
+// weights [rows, experts] float32.
+JLLM_EXPORT int jllm_route_experts(const void* h, int dtype, int ld, const float* router, const void* correction,
+                                   int correction_dtype, float* weights, int rows, int dim, int experts, int top, float scale,
+                                   int normalize, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0 && experts > 0 && top >= 1 && top <= experts && experts <= 4096,
+                 "route_experts: rows=%d dim=%d experts=%d top=%d", rows, dim, experts, top);
+    if (rows == 0) return JLLM_OK;
+    const VecRef c{correction, correction_dtype};
+    const size_t smem = 2 * (size_t)experts * sizeof(float);
+    if (dtype == JLLM_F32)
+        jllm_launch(route_experts_kernel<float>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT, (const float*)h, ld,
+                    router, c, (int)(correction != nullptr), weights, dim, experts, top, scale, normalize);
+    else
+        jllm_launch(route_experts_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT,
+                    (const __nv_bfloat16*)h, ld, router, c, (int)(correction != nullptr), weights, dim, experts, top, scale,
+                    normalize);
+    return jllm_check_launch("route_experts");
+}
+
+// hidden [rows, experts * ff] (contiguous): the values of expert e are multiplied by weights[r, e].
+JLLM_EXPORT int jllm_scale_expert_hidden(void* hidden, int dtype, const float* weights, int rows, int experts, int ff,
+                                         cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0, "scale_expert_hidden: rows=%d experts=%d ff=%d", rows, experts, ff);
+    if (rows == 0) return JLLM_OK;
+    const size_t total = (size_t)rows * experts * ff;
+    const int blocks = (int)min((size_t)65535, (total + 255) / 256);
+    if (dtype == JLLM_F32)
+        jllm_launch(scale_expert_hidden_kernel<float>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (float*)hidden,
+                    weights, experts, ff, total);
+    else
+        jllm_launch(scale_expert_hidden_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
+                    (__nv_bfloat16*)hidden, weights, experts, ff, total);
+    return jllm_check_launch("scale_expert_hidden");
+}

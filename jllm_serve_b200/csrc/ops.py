@@ -152,6 +152,16 @@ class _Signatures:
     jllm_attention_decode_separate_combine = [I]
     jllm_attention_decode_fresh = [P, I, P, P, I, I, F, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
     jllm_argmax = [P, I, I, I, P, P]
+    jllm_bounds_error_linear_attention = [P]
+    jllm_bounds_error_latent_attention = [P]
+    jllm_dynamic_tanh = [P, P, P, I, F, P, I, P, I, I, P]
+    jllm_add_scaled = [P, P, F, ctypes.c_longlong, P]
+    jllm_gla_recurrent = [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P]
+    jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, P]
+    jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
+    jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, P]
+    jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, P]
+    jllm_scale_expert_hidden = [P, I, P, I, I, I, P]
     jllm_sample = [P, I, I, I, P, P, P, P, P, P, P]
 
 
@@ -178,6 +188,78 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, 
     n = (row_index.numel() if row_index is not None else x.shape[0]) if rows is None else rows
     _call("jllm_rmsnorm", x.data_ptr(), gain.data_ptr(), _DT[gain.dtype], out.data_ptr(), _DT[out.dtype],
           _p(row_index), n, x.shape[-1], float(eps), _stream())
+
+
+def dynamic_tanh(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: float, out: torch.Tensor,
+                 row_index: torch.Tensor | None = None, rows: int | None = None) -> None:
+    """out[r] = tanh(alpha * x[row_index[r] or r]) * weight + bias; x float32 [*, dim]; out float32 or bfloat16."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and weight.dtype == bias.dtype
+    n = (row_index.numel() if row_index is not None else x.shape[0]) if rows is None else rows
+    _call("jllm_dynamic_tanh", x.data_ptr(), weight.data_ptr(), bias.data_ptr(), _DT[weight.dtype], float(alpha),
+          out.data_ptr(), _DT[out.dtype], _p(row_index), n, x.shape[-1], _stream())
+
+
+def add_scaled(x: torch.Tensor, y: torch.Tensor, scale: float) -> None:
+    """x += scale * y, both float32 and contiguous, of one shape."""
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and x.shape == y.shape
+    _call("jllm_add_scaled", x.data_ptr(), y.data_ptr(), float(scale), x.numel(), _stream())
+
+
+def gla_recurrent(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg_len, state_slots, out, heads, key_dim,
+                  value_dim, query_scale, temperature) -> None:
+    """Gated linear attention over the segments of a step: per head S = diag(d) S + k v^T, o = S^T (query_scale q), d =
+    sigmoid(decay_logits)^(1 / temperature). proj [rows, *]: q, k (heads x key_dim) and v (heads x value_dim) at the
+    given columns; decay_logits [rows, heads x key_dim] float32; state [slots, heads, key_dim, value_dim] float32, read
+    and written in place at `state_slots[segment]`; out [rows, heads x value_dim] float32."""
+    assert decay_logits.dtype == state.dtype == out.dtype == torch.float32 and proj.stride(1) == 1
+    assert decay_logits.is_contiguous() and state.is_contiguous() and out.is_contiguous()
+    _call("jllm_gla_recurrent", proj.data_ptr(), _DT[proj.dtype], proj.stride(0), q_off, k_off, v_off,
+          decay_logits.data_ptr(), state.data_ptr(), state.shape[0], seg_start.data_ptr(), seg_len.data_ptr(),
+          state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), heads, key_dim, value_dim, float(query_scale),
+          float(temperature), _stream())
+
+
+def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim) -> None:
+    """out[r, h] = rmsnorm(o[r, h]) * gain * silu(gate[r, h]) * scale over every head's value_dim values; o float32
+    [rows, heads x value_dim], gate a view [rows, heads x value_dim] with any row stride, out contiguous like gate's type."""
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and gate.dtype == out.dtype
+    _call("jllm_gated_head_norm", o.data_ptr(), gate.data_ptr(), _DT[gate.dtype], gate.stride(0), gain.data_ptr(),
+          _DT[gain.dtype], out.data_ptr(), o.shape[0], heads, value_dim, float(eps), float(scale), _stream())
+
+
+def latent_norm_store(src, gain, eps, slots, cache) -> None:
+    """cache row slots[r] = rmsnorm(src[r]) * gain; src a view [rows, rank]; cache [pages, 1, page_size, rank]."""
+    assert src.dtype == cache.dtype and src.stride(1) == 1 and cache.is_contiguous() and slots.dtype == torch.int32
+    rank = src.shape[1]
+    _call("jllm_latent_norm_store", src.data_ptr(), _DT[src.dtype], src.stride(0), gain.data_ptr(), _DT[gain.dtype],
+          slots.data_ptr(), cache.data_ptr(), cache.numel() // rank, src.shape[0], rank, float(eps), _stream())
+
+
+def gemm_heads(a, w, out, gate=None, alpha: float = 1.0) -> None:
+    """out[r, h, :] = f * w[h] @ a[r, h, :] for all heads at once; a [rows, heads x K] (any row stride), w [heads, N, K]
+    contiguous, out [rows, heads x N]; f = alpha, or alpha * sigmoid(gate[r, h]) with gate a view [rows, heads]."""
+    heads, N, K = w.shape
+    assert a.dtype == w.dtype == out.dtype and w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
+    assert a.shape[1] == heads * K and out.shape[1] == heads * N and (gate is None or gate.dtype == a.dtype)
+    _call("jllm_gemm_heads", a.data_ptr(), _DT[a.dtype], a.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
+          _p(gate), gate.stride(0) if gate is not None else 0, float(alpha), a.shape[0], heads, N, K, _stream())
+
+
+def route_experts(h, router, correction, top, scale, normalize, weights) -> None:
+    """weights[r, e] = the weight of expert e for row r (0 where it is not among the row's `top`): scores sigmoid(router
+    h) in float32, choice by score + correction, chosen scores over their sum (+ 1e-20) if `normalize`, times scale."""
+    assert router.dtype == torch.float32 and router.is_contiguous() and weights.dtype == torch.float32
+    assert weights.is_contiguous() and h.stride(1) == 1 and weights.shape == (h.shape[0], router.shape[0])
+    _call("jllm_route_experts", h.data_ptr(), _DT[h.dtype], h.stride(0), router.data_ptr(), _p(correction),
+          _DT[correction.dtype] if correction is not None else F32, weights.data_ptr(), h.shape[0], h.shape[1],
+          router.shape[0], int(top), float(scale), int(bool(normalize)), _stream())
+
+
+def scale_expert_hidden(hidden, weights, ff) -> None:
+    """hidden[r, e * ff + j] *= weights[r, e], in place; hidden contiguous [rows, experts x ff]."""
+    assert hidden.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
+    _call("jllm_scale_expert_hidden", hidden.data_ptr(), _DT[hidden.dtype], weights.data_ptr(), hidden.shape[0],
+          weights.shape[1], int(ff), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -449,7 +531,7 @@ def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swigl
 
 
 BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",
-                "attention_prefill_pair", "rowwise")
+                "attention_prefill_pair", "rowwise", "linear_attention", "latent_attention")
 BOUNDS_WHAT = {1: "a block-table index", 2: "a page id", 3: "a cache slot", 4: "a token id", 5: "a row"}
 
 

@@ -148,6 +148,55 @@ JLLM_EXPORT int jllm_rmsnorm(const float* x, const void* gain, int gain_dtype, v
 }
 
 // ---------------------------------------------------------------------------------------------------
+// Dynamic Tanh: out[r] = tanh(a * x[src(r)]) * w + b, src(r) = row_index ? row_index[r] : r. A norm without statistics:
+// no mean, no variance, no reduction; a is one scalar per norm.
+// ---------------------------------------------------------------------------------------------------
+template <typename Tout>
+__global__ void __launch_bounds__(256)
+dynamic_tanh_kernel(const float* __restrict__ x, VecRef w, VecRef b, float a, Tout* __restrict__ out,
+                    const int* __restrict__ row_index, int dim) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const float* src = x + (size_t)(row_index ? row_index[r] : r) * dim;
+    Tout* dst = out + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        dst[i] = from_float<Tout>(__fadd_rn(__fmul_rn(tanhf(__fmul_rn(a, src[i])), w[i]), b[i]));
+}
+
+JLLM_EXPORT int jllm_dynamic_tanh(const float* x, const void* w, const void* b, int vec_dtype, float a, void* out,
+                                  int out_dtype, const int* row_index, int rows, int dim, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0, "dynamic_tanh: rows=%d dim=%d", rows, dim);
+    if (rows == 0) return JLLM_OK;
+    const VecRef wv{w, vec_dtype}, bv{b, vec_dtype};
+    if (out_dtype == JLLM_F32)
+        jllm_launch(dynamic_tanh_kernel<float>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, wv, bv, a, (float*)out,
+                    row_index, dim);
+    else
+        jllm_launch(dynamic_tanh_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, wv, bv, a,
+                    (__nv_bfloat16*)out, row_index, dim);
+    return jllm_check_launch("dynamic_tanh");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// x += scale * y (float32, elementwise): the residual sum of a part that cannot scale its own result
+// ---------------------------------------------------------------------------------------------------
+__global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict__ y, float scale, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = fmaf(scale, y[i], x[i]);
+}
+
+JLLM_EXPORT int jllm_add_scaled(float* x, const float* y, float scale, long long total, cudaStream_t stream) {
+    JLLM_REQUIRE(total >= 0, "add_scaled: total=%lld", total);
+    if (total == 0) return JLLM_OK;
+    const int blocks = (int)min((long long)65535, (total + 255) / 256);
+    jllm_launch(add_scaled_kernel, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, y, scale, (size_t)total);
+    return jllm_check_launch("add_scaled");
+}
+
+// ---------------------------------------------------------------------------------------------------
 // SwiGLU: h[r, j] = silu(gate_up[r, j]) * gate_up[r, hidden + j],  silu(g) = g / (1 + exp(-g))
 // ---------------------------------------------------------------------------------------------------
 template <typename T>

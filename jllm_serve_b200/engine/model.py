@@ -20,6 +20,13 @@ from ..parts import Linear, RunCache, Runtime, part_class
 from ..weights.loader import TensorWant
 
 
+def cls_prefix(layer, names, index: int) -> str:
+    """The checkpoint prefix of a layer: its own if the spec names one (a model whose layers are not numbered in the
+    order of their specs), else the model's pattern with the layer's index."""
+    own = getattr(layer, "prefix", None)
+    return own if own is not None else names.layer.format(index)
+
+
 class DecoderModel:
     def __init__(self, spec: Decoder, tensors: Dict[str, torch.Tensor], runtime: Runtime):
         self.spec, self.rt = spec, runtime
@@ -38,7 +45,7 @@ class DecoderModel:
         self.blocks = []
         for l, layer in enumerate(spec.layers):
             cls = part_class("block", layer.arrangement)
-            self.blocks.append(cls(layer, core.dim, tensors, names.layer.format(l), runtime, self.position_encodings))
+            self.blocks.append(cls(layer, core.dim, tensors, cls_prefix(layer, names, l), runtime, self.position_encodings))
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, core.dim, tensors,
                                                                    names.final_norm, runtime)
         self.vocab, self.dim = core.vocab, core.dim
@@ -52,7 +59,7 @@ class DecoderModel:
         for t in spec.rope_tables:
             out.update(part_class("position", t.kind).wants(t, core.dim, ""))
         for l, layer in enumerate(spec.layers):
-            out.update(part_class("block", layer.arrangement).wants(layer, core.dim, names.layer.format(l)))
+            out.update(part_class("block", layer.arrangement).wants(layer, core.dim, cls_prefix(layer, names, l)))
         out.update(part_class("norm", spec.final_norm.kind).wants(spec.final_norm, core.dim, names.final_norm))
         return out
 

@@ -17,7 +17,7 @@ import torch
 
 from ..cache import CacheManager, PoolExhausted
 from ..cache.budget import DEFAULT_SHARE, plan_pages
-from ..config.registry import architecture_entry, load_config, parse_config
+from ..config.registry import architecture_entry, load_config, model_type_of, parse_config
 from ..csrc import ops
 from ..parts import Runtime
 from ..weights import TensorSource, convert_checked, load_checked, random_tensors
@@ -60,7 +60,7 @@ class ModelRunner:
         if schedule is not None:
             spec = spec.with_schedule(schedule)
         self.spec, self.config = spec, raw
-        entry = architecture_entry(raw["model_type"])
+        entry = architecture_entry(model_type_of(raw))
         self.ctx = int(ctx or spec.core.max_positions)
         self.page_size = int(page_size)
         self.max_rows = int(max_batch_tokens)

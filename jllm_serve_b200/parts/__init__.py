@@ -2,8 +2,11 @@
 from .base import (Block, FeedForward, Mixer, Norm, Part, PositionEncoding, RunCache, Runtime, part_class,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position_encoding)
 from .linear import Linear
-from .norm import RmsNorm
+from .norm import DynamicTanh, RmsNorm
 from .rope import RotaryTable
 from .attention import GqaAttention
 from .mlp import DenseGlu
+from .linear_attention import GatedLinearAttention
+from .latent_attention import LatentAttention
+from .experts import RoutedExperts
 from .block import PreNormBlock

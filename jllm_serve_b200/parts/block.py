@@ -4,9 +4,17 @@
 959-969): x += mixer(norm(x)); x += feed_forward(norm(x)), no norms after the parts. The
 residual stream x is float32 in both precisions; the parts add into it themselves (the add
 is the epilogue of their last matrix product).
+
+Two things a layer spec may say beyond that: `feed_forward=None` (the layer is its mixer alone, and has no second
+norm), and `residual_scale` s (x += s * part(norm(x))). A part that can scale its own result says so
+(`takes_residual_scale`; it gets the factor as `residual_scale` and applies it in front of its last product); any other
+part adds into a zeroed float32 buffer instead, which is then added to x with the factor.
 """
 from __future__ import annotations
 
+import torch
+
+from ..csrc import ops
 from .base import Block, part_class, register_block
 
 
@@ -16,17 +24,29 @@ class PreNormBlock(Block):
         norm_cls = part_class("norm", spec.norm.kind)
         self.rt, self.dim = runtime, dim
         self.mixer_norm = norm_cls(spec.norm, dim, tensors, prefix + names.mixer_norm, runtime)
-        self.ffn_norm = norm_cls(spec.norm, dim, tensors, prefix + names.feed_forward_norm, runtime)
         mixer_cls = part_class("mixer", spec.mixer.kind)
         table = getattr(spec.mixer, "rope_table", -1)
         extra = {"rope": position_encodings[table]} if table is not None and table >= 0 and position_encodings else {}
         self.mixer = mixer_cls(spec.mixer, dim, tensors, prefix + names.mixer, runtime, **extra)
-        self.feed_forward = part_class("feed_forward", spec.feed_forward.kind)(
-            spec.feed_forward, dim, tensors, prefix + names.feed_forward, runtime)
+        self.ffn_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ffn_norm = norm_cls(spec.norm, dim, tensors, prefix + names.feed_forward_norm, runtime)
+            self.feed_forward = part_class("feed_forward", spec.feed_forward.kind)(
+                spec.feed_forward, dim, tensors, prefix + names.feed_forward, runtime)
+        self.scale = float(getattr(spec, "residual_scale", 1.0))
+        self._scaled_outside = set()
+        for part in (self.mixer, self.feed_forward):
+            if part is None or self.scale == 1.0:
+                continue
+            if getattr(part, "takes_residual_scale", False):
+                part.residual_scale = self.scale
+            else:
+                self._scaled_outside.add(id(part))
 
     @property
     def graph_safe(self) -> bool:
-        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.ffn_norm, self.mixer, self.feed_forward))
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.ffn_norm, self.mixer, self.feed_forward)
+                   if p is not None)
 
     def decode_bucket_cap(self, rows: int) -> int:
         # (norms and feed-forwards do not look at the bucket; a mixer that does not say gets the safe answer)
@@ -38,18 +58,37 @@ class PreNormBlock(Block):
         norm_cls = part_class("norm", spec.norm.kind)
         out = {}
         out.update(norm_cls.wants(spec.norm, dim, prefix + names.mixer_norm))
-        out.update(norm_cls.wants(spec.norm, dim, prefix + names.feed_forward_norm))
         out.update(part_class("mixer", spec.mixer.kind).wants(spec.mixer, dim, prefix + names.mixer))
-        out.update(part_class("feed_forward", spec.feed_forward.kind).wants(spec.feed_forward, dim,
-                                                                            prefix + names.feed_forward))
+        if spec.feed_forward is not None:
+            out.update(norm_cls.wants(spec.norm, dim, prefix + names.feed_forward_norm))
+            out.update(part_class("feed_forward", spec.feed_forward.kind).wants(spec.feed_forward, dim,
+                                                                                prefix + names.feed_forward))
         return out
+
+    def _into(self, part, x):
+        """Where `part` adds its result: x itself, or a zeroed buffer that `_settle` adds to x with the layer's factor."""
+        if id(part) not in self._scaled_outside:
+            return x
+        y = self.rt.buffer("residual_part", self.dim, torch.float32)[:x.shape[0]]
+        y.zero_()
+        return y
+
+    def _settle(self, x, y) -> None:
+        if y is not x:
+            ops.add_scaled(x, y, self.scale)
 
     def forward(self, x, batch, cache) -> None:
         xb = self.rt.buffer("normed", self.dim)[:x.shape[0]]
         self.mixer_norm.forward(x, xb)
-        self.mixer.forward(xb, x, batch, cache)
+        y = self._into(self.mixer, x)
+        self.mixer.forward(xb, y, batch, cache)
+        self._settle(x, y)
+        if self.feed_forward is None:
+            return
         self.ffn_norm.forward(x, xb)
-        self.feed_forward.forward(xb, x, batch)
+        y = self._into(self.feed_forward, x)
+        self.feed_forward.forward(xb, y, batch)
+        self._settle(x, y)
 
 
 register_block("pre_norm", PreNormBlock, replace=True)

@@ -27,3 +27,26 @@ class RmsNorm(Norm):
 
 
 register_norm("rmsnorm", RmsNorm, replace=True)
+
+
+class DynamicTanh(Norm):
+    """y = tanh(a * x) * w + b: a norm without statistics (no mean, no variance, no eps), `a` one stored scalar. The
+    tensors lie beside one another under the norm's own name: `<name>` (w), `<name>.b`, `<name>.alpha`."""
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
+        self.dim = dim
+        self.weight, self.bias = tensors[prefix], tensors[prefix + ".b"]
+        if self.bias.dtype != self.weight.dtype:
+            self.bias = self.bias.to(self.weight.dtype)
+        self.alpha = float(tensors[prefix + ".alpha"].float().item())
+
+    @classmethod
+    def wants(cls, spec, dim: int, prefix: str) -> dict:
+        return {prefix: TensorWant((dim,), "vector", init="gain"), prefix + ".b": TensorWant((dim,), "vector"),
+                prefix + ".alpha": TensorWant((), "vector", init="gain")}
+
+    def forward(self, x, out, row_index=None, rows=None):
+        ops.dynamic_tanh(x, self.weight, self.bias, self.alpha, out, row_index, rows)
+
+
+register_norm("dynamic_tanh", DynamicTanh, replace=True)

@@ -33,9 +33,15 @@ class WeightError(ValueError):
         self.missing, self.unexpected, self.wrong_shape = list(missing), list(unexpected), list(wrong_shape)
 
 
+def shape_fits(has, want) -> bool:
+    """Whether a stored shape is the wanted one; a wanted size of -1 stands for "whatever the checkpoint has"."""
+    has, want = tuple(has), tuple(want)
+    return len(has) == len(want) and all(w == -1 or h == w for h, w in zip(has, want))
+
+
 @dataclass(frozen=True)
 class TensorWant:
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]                 # a size of -1: the checkpoint's own (the part reads it from the tensor)
     role: str = "matrix"                   # matrix | matrix_fp32 | vector | int_table
     optional: bool = False
     init: str = "normal"                   # random-weights mode: normal = N(0, 0.02), gain = 1 + N(0, 0.1)
@@ -87,7 +93,7 @@ def compare(source_meta: Dict[str, Tuple[torch.dtype, Tuple[int, ...]]], wants: 
     missing = sorted(n for n, w in wants.items() if n not in source_meta and not w.optional)
     unexpected = sorted(n for n in source_meta if n not in wants)
     wrong = sorted((n, tuple(source_meta[n][1]), tuple(w.shape)) for n, w in wants.items()
-                   if n in source_meta and tuple(source_meta[n][1]) != tuple(w.shape))
+                   if n in source_meta and not shape_fits(source_meta[n][1], w.shape))
     if not (missing or wrong or (strict and unexpected)):
         return unexpected
     lines = [f"{where}: the tensors do not match the configuration"]

@@ -35,6 +35,9 @@ def random_tensors(wants: Dict[str, TensorWant], seed: int, device="cpu", dtype:
     out = {}
     gen = torch.Generator(device=device)
     for name, want in wants.items():
+        if any(n < 0 for n in want.shape):
+            raise ValueError(f"{name}: the configuration leaves a size of this tensor to the checkpoint "
+                             f"({list(want.shape)}); random weights need it named")
         gen.manual_seed(_seed_for(seed, name))
         t = torch.randn(want.shape, generator=gen, device=device, dtype=torch.float32)
         t = t * GAIN_STD + 1.0 if want.init == "gain" else t * MATRIX_STD
@@ -46,11 +49,11 @@ def random_tensors(wants: Dict[str, TensorWant], seed: int, device="cpu", dtype:
 def write_model_folder(config: dict, seed: int, out_dir, dtype: torch.dtype = torch.bfloat16,
                        vector_dtype: torch.dtype | None = None) -> Path:
     """config.json + model.safetensors of random weights for `config` (a dict with the architecture's own keys)."""
-    from ..config.registry import architecture_entry, parse_config
+    from ..config.registry import architecture_entry, model_type_of, parse_config
     from ..engine.model import model_wants
 
     spec = parse_config(config)
-    wants = model_wants(architecture_entry(config["model_type"]), spec)
+    wants = model_wants(architecture_entry(model_type_of(config)), spec)
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     (out_dir / "config.json").write_text(json.dumps(config, indent=2))
