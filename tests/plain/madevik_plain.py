@@ -165,3 +165,11 @@ def forward(cfg, w, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return dyt(x, w, "final.norm") @ w["head"].T
+
+
+def greedy_generate(cfg, w, prompt, n):
+    """`n` tokens chosen greedily (the lowest index wins a tie), the whole sequence run anew for every token."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(forward(cfg, w, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
