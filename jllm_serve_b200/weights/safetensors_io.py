@@ -165,7 +165,7 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata: Dict[str
         t = t.detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot write tensor {name!r} of dtype {t.dtype}")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""     # (a scalar has no last dimension to view)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
         blobs.append(raw)

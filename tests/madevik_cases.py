@@ -49,21 +49,26 @@ MADEVIK = {"P": MADEVIK_P, "Q": MADEVIK_Q, "R": MADEVIK_R}
 
 
 def sharpen(tensors: dict, config: dict) -> dict:
-    """Random weights of N(0, 0.02) make every attention nearly uniform and every decay nearly 1/2^(1/tau): a lost key or
-    a wrong state would hardly show. Queries are scaled up so that single keys stand out, the decay's bias is spread so
-    that some channels remember for hundreds of tokens and others forget at once, and the router's corrections are
-    large enough to change the choice."""
+    """Random weights of N(0, 0.02) leave every activation tiny: every attention nearly uniform, every decay nearly the
+    same, the mixers a rounding error beside the embedding; a lost key or a stale state would not show. Here every
+    matrix is rescaled so that unit inputs give unit outputs (N(0, 1 / fan-in)) and the embedding to N(0, 1); queries are
+    scaled up further so that single keys stand out among hundreds, the decay's bias is spread so that some channels
+    remember for hundreds of tokens and others forget at once, and the router's corrections are large enough to change
+    the choice."""
     out = dict(tensors)
     g = torch.Generator().manual_seed(5)
     for name, t in tensors.items():
-        if name.endswith("mix.q") or name.endswith("mix.uk") or name.endswith("mix.k"):
-            out[name] = (t.float() * 12.0).to(t.dtype)
+        if name == "embed":
+            out[name] = (t.float() * 50.0).to(t.dtype)
+        elif t.dim() == 2:
+            gain = 3.0 if name.endswith("mix.q") else 1.0
+            out[name] = (t.float() * (gain / (0.02 * t.shape[1] ** 0.5))).to(t.dtype)
         elif name.endswith("mix.a2.b"):
             out[name] = (torch.randn(t.shape, generator=g) * 4.0 + 2.0).to(t.dtype)
         elif name.endswith("mlp.correction"):
             out[name] = (torch.randn(t.shape, generator=g) * 0.3).to(t.dtype)
-        elif name.endswith("mlp.router") or name.endswith("mix.g"):
-            out[name] = (t.float() * 20.0).to(t.dtype)
+        elif name.endswith(".b"):
+            out[name] = (t.float() * 10.0).to(t.dtype)
     return out
 
 
