@@ -13,6 +13,11 @@ read (every weight once plus the cache of the live requests) with the measured c
 `points` holds decode at batch 1 and 64; `check` compares the bfloat16 logits with the 32-bit path's at these
 layer sizes (two layers, untimed). Peaks come from MEASURED_PEAKS.json when it exists.
 
+`--design madevik` is another program under the same roof and leaves the default workload alone: prefill and decode of
+the Madevik design (gated linear attention, attention over a cached latent, routed experts) at layer sizes that resemble
+a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
+picks among them); one JSON line with both models' figures per size.
+
 The engine runs on one GPU; for --gpus above 1 the program says so and exits with 2.
 """
 from __future__ import annotations
@@ -104,8 +109,134 @@ def model_numbers(cfg: dict, layers: int) -> dict:
             "attn_flops_per_layer": lambda T: 4 * (T * (T + 1) // 2) * H * hd}
 
 
+def _moe(experts, top, ff):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 2.0}}
+
+
+def madevik_shape(width, heads, rank, experts, top, ff, runs, vocab=32768):
+    """Three linear-attention layers to one latent-attention layer, head size 128 throughout."""
+    mlp = _moe(experts, top, ff)
+    gla = {"type": "gla", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}, "mlp": mlp}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": rank, "scale": 128 ** -0.5}, "mlp": mlp}
+    return {"architecture": "Madevik", "width": width, "vocab": vocab, "residual_mult": 0.5, "norm": {"eps": 1e-5},
+            "layers": [latent if i % 4 == 3 else gla for i in range(runs)]}
+
+
+# name -> (Madevik configuration, the Qwen3 dense shape of the same width, heads, layers and feed-forward weights)
+DESIGN_SIZES = {
+    "w2048": (madevik_shape(2048, 16, 128, 8, 2, 1024, 8),
+              dict(QWEN3_8B, hidden_size=2048, num_hidden_layers=8, num_attention_heads=16, num_key_value_heads=8,
+                   intermediate_size=8192, vocab_size=32768)),
+    "w4096": (madevik_shape(4096, 32, 256, 16, 4, 768, 4),
+              dict(QWEN3_8B, hidden_size=4096, num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=8,
+                   intermediate_size=12288, vocab_size=32768)),
+}
+
+
+def design_bench(args) -> int:
+    """Prefill of one prompt and decode steps of a batch, device-timed, for the Madevik design and the Qwen3 dense shape
+    beside it. Decode: `--batch` requests whose contexts (synthetic cache content, zero states) stand at `--context`."""
+    import torch
+
+    from jllm_serve_b200.csrc import ops
+    from jllm_serve_b200.engine import Engine, Segment
+
+    ctx, batch, tokens = min(args.context, 2048), args.batch, min(PREFILL_TOKENS, args.context)
+    steps, warmup = max(8, args.steps // 2), max(3, args.warmup)
+    out = {"design": "madevik", "dtype": "bf16", "data": "synthetic token ids, random-init weights", "prefill_tokens": tokens,
+           "decode_batch": batch, "decode_context": ctx, "steps": steps, "warmup": warmup, "sizes": {}}
+    out_tok = torch.empty(max(64, batch), dtype=torch.int32, device="cuda:0")
+    for name in args.design_sizes.split(","):
+        if name not in DESIGN_SIZES:
+            print(f"bench.py: unknown size {name!r} (known: {', '.join(sorted(DESIGN_SIZES))})")
+            return 2
+        record = {}
+        for model, cfg in zip(("madevik", "qwen3"), DESIGN_SIZES[name]):
+            engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx + 64, page_size=PAGE,
+                            num_pages=((batch + 1) * (ctx + 64) + 2 * tokens) // PAGE, max_batch_tokens=tokens + 64,
+                            chunk=tokens, max_running=batch + 2)
+            runner = engine.runner
+            print(f"bench: {runner.describe()}", file=sys.stderr, flush=True)
+            for g in runner.cache.paged:
+                g.storage.normal_()
+            gen = torch.Generator().manual_seed(1)
+            prompt = torch.randint(0, runner.vocab, (tokens,), generator=gen).tolist()
+            times = []
+            for i in range(7):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                runner.step([Segment(f"p{i}", prompt, 0, [tokens - 1])])
+                e.record()
+                torch.cuda.synchronize()
+                runner.finish(f"p{i}")
+                times.append(s.elapsed_time(e))
+            pre_ms = statistics.median(times[2:])
+            ids = [f"d{i}" for i in range(batch)]
+            start = ctx - warmup - steps
+            for i in ids:
+                runner.cache.open(i)
+                runner.cache.reserve(i, 0, start)
+                runner.cache.commit(i, start)
+
+            def one_step():
+                logits = runner.step([Segment(i, [1 + k], runner.cache.length(i), [0]) for k, i in enumerate(ids)])
+                ops.argmax(logits, out_tok[:batch])
+
+            for _ in range(warmup):
+                one_step()
+            torch.cuda.synchronize()
+            before = ops.launch_count
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(steps):
+                one_step()
+            e.record()
+            torch.cuda.synchronize()
+            dec_ms = s.elapsed_time(e) / steps
+            launches = (ops.launch_count - before) // steps
+            for i in ids:
+                runner.finish(i)
+            weights = sum(t.numel() * t.element_size() for t in _tensors_of(runner.model))
+            record[model] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(tokens / pre_ms * 1e3, 1),
+                             "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(batch * 1e3 / dec_ms, 1),
+                             "kernels_per_decode_step": launches, "weight_gb": round(weights / 1e9, 3),
+                             "layers": len(runner.spec.schedule)}
+            engine.close()
+            del engine, runner
+            torch.cuda.empty_cache()
+        out["sizes"][name] = record
+    print(json.dumps(out))
+    return 0
+
+
+def _tensors_of(obj, seen=None):
+    """Every device tensor reachable from a model's parts (weights, packed or plain), each once."""
+    import torch
+    seen = set() if seen is None else seen
+    if id(obj) in seen:
+        return
+    seen.add(id(obj))
+    if isinstance(obj, torch.Tensor):
+        if obj.is_cuda and obj.data_ptr() not in seen:
+            seen.add(obj.data_ptr())
+            yield obj
+    elif isinstance(obj, (list, tuple)):
+        for v in obj:
+            yield from _tensors_of(v, seen)
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            yield from _tensors_of(v, seen)
+    elif hasattr(obj, "__dict__") and type(obj).__module__.startswith("jllm_serve_b200") and type(obj).__name__ != "Runtime":
+        for v in vars(obj).values():
+            yield from _tensors_of(v, seen)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--design", default="", choices=["", "madevik"],
+                    help="madevik: time the Madevik design beside the Qwen3 dense shape of equal size instead of the default workload")
+    ap.add_argument("--design-sizes", default="w2048,w4096", help="which of the sizes of --design, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
@@ -137,6 +268,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.design:
+        return design_bench(args)
 
     import torch
 

@@ -16,15 +16,29 @@ route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ 
                      float* __restrict__ weights, int dim, int experts, int top, float scale, int normalize) {
     extern __shared__ float smem[];
     float* s = smem;                   // [experts] scores
-    float* c = s + experts;            // [experts] choice scores, -inf once taken
+    float* c = s + (experts + 1) / 2 * 2;      // [experts] choice scores, -inf once taken
+    float* hs = c + (experts + 1) / 2 * 2;     // [dim] the row, read once (on a 16-byte boundary)
     pdl_wait();
     pdl_trigger();
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const T* row = h + (size_t)r * ld;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) hs[i] = to_float(row[i]);
+    __syncthreads();
+    const bool vec = (dim & 3) == 0 && (((uintptr_t)router) & 15u) == 0;
     for (int e = warp; e < experts; e += warps) {
         const float* wr = router + (size_t)e * dim;
         float acc = 0.f;
-        for (int i = lane; i < dim; i += 32) acc = fmaf(to_float(row[i]), wr[i], acc);
+        if (vec) {      // a lane takes four neighbouring values at a time; the order of the sum is fixed all the same
+            for (int i = lane * 4; i < dim; i += 128) {
+                const float4 a = *reinterpret_cast<const float4*>(hs + i), b = *reinterpret_cast<const float4*>(wr + i);
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+                acc = fmaf(a.z, b.z, acc);
+                acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (int i = lane; i < dim; i += 32) acc = fmaf(hs[i], wr[i], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) {
             const float sc = 1.f / (1.f + expf(-acc));
@@ -64,6 +78,25 @@ __global__ void scale_expert_hidden_kernel(T* __restrict__ hidden, const float* 
     }
 }
 
+// The same, 16 bytes a thread (ff a multiple of the 16-byte group: a group lies inside one expert).
+template <typename T>
+__global__ void scale_expert_hidden_vec_kernel(T* __restrict__ hidden, const float* __restrict__ weights, int experts, int ff,
+                                               size_t groups) {
+    constexpr int N = 16 / sizeof(T);
+    pdl_wait();
+    pdl_trigger();
+    const size_t width = (size_t)experts * ff;
+    for (size_t gi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; gi < groups; gi += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = gi * N, r = i / width, col = i - r * width;
+        const float wt = weights[r * experts + col / ff];
+        uint4 raw = *reinterpret_cast<const uint4*>(hidden + i);
+        T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[k] = from_float<T>(__fmul_rn(to_float(v[k]), wt));
+        *reinterpret_cast<uint4*>(hidden + i) = raw;
+    }
+}
+
 }  // namespace
 
 // h [rows, ld] of type `dtype` (the normed rows); router [experts, dim] float32; correction [experts] or null;
@@ -75,7 +108,14 @@ JLLM_EXPORT int jllm_route_experts(const void* h, int dtype, int ld, const float
                  "route_experts: rows=%d dim=%d experts=%d top=%d", rows, dim, experts, top);
     if (rows == 0) return JLLM_OK;
     const VecRef c{correction, correction_dtype};
-    const size_t smem = 2 * (size_t)experts * sizeof(float);
+    const int padded = (experts + 1) / 2 * 2;       // the row's copy behind the two score arrays starts on 16 bytes
+    const size_t smem = (2 * (size_t)padded + dim) * sizeof(float);
+    JLLM_REQUIRE(smem <= 200 * 1024, "route_experts: dim=%d and experts=%d need %zu bytes of shared memory", dim, experts, smem);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(route_experts_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(route_experts_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return jllm_fail(JLLM_CUDA_ERROR, "route_experts: %zu bytes of shared memory refused", smem);
+    }
     if (dtype == JLLM_F32)
         jllm_launch(route_experts_kernel<float>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT, (const float*)h, ld,
                     router, c, (int)(correction != nullptr), weights, dim, experts, top, scale, normalize);
@@ -92,6 +132,18 @@ JLLM_EXPORT int jllm_scale_expert_hidden(void* hidden, int dtype, const float* w
     JLLM_REQUIRE(rows >= 0 && experts > 0 && ff > 0, "scale_expert_hidden: rows=%d experts=%d ff=%d", rows, experts, ff);
     if (rows == 0) return JLLM_OK;
     const size_t total = (size_t)rows * experts * ff;
+    const int per = dtype == JLLM_F32 ? 4 : 8;
+    if (ff % per == 0 && ((uintptr_t)hidden % 16) == 0) {
+        const size_t groups = total / per;
+        const int vblocks = (int)min((size_t)65535, (groups + 255) / 256);
+        if (dtype == JLLM_F32)
+            jllm_launch(scale_expert_hidden_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
+                        (float*)hidden, weights, experts, ff, groups);
+        else
+            jllm_launch(scale_expert_hidden_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, LAUNCH_DEPENDENT,
+                        (__nv_bfloat16*)hidden, weights, experts, ff, groups);
+        return jllm_check_launch("scale_expert_hidden");
+    }
     const int blocks = (int)min((size_t)65535, (total + 255) / 256);
     if (dtype == JLLM_F32)
         jllm_launch(scale_expert_hidden_kernel<float>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (float*)hidden,

@@ -7,9 +7,11 @@
 // (kv_heads = 1, head_dim = rank). Here:
 //
 //   latent_norm_store   RMSNorm of the down-projected rows (float32 arithmetic) and their write into the paged cache
-//   gemm_heads          out[r, h, :] = f(r, h) * W[h] a[r, h, :] for every head h at once (W [heads, N, K]), on the CUDA
-//                       cores with one float32 accumulator per element in ascending k, so that a row's result does not
-//                       depend on the batch; f = alpha, or alpha * sigmoid(gate[r, h]) (the mixer's output gate)
+//   gemm_heads          out[r, h, :] = f(r, h) * W[h] a[r, h, :] for every head h at once (W [heads, N, K]); f = alpha, or
+//                       alpha * sigmoid(gate[r, h]) (the mixer's output gate). float32: on the CUDA cores with one
+//                       accumulator per element in ascending k. bfloat16: 64 x 64 tiles per (head, block) on the tensor
+//                       cores (mma.sync m16n8k16, float32 accumulation), operands staged in shared memory 32 k at a
+//                       time. Either way a row's result depends on that row alone, not on the batch.
 #include "common.cuh"
 
 namespace {
@@ -94,6 +96,90 @@ gemm_heads_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, T* 
     }
 }
 
+// The bfloat16 product on the tensor cores. Four warps; warp w holds rows [16 w, 16 w + 16) of the block's 64 x 64 tile
+// as eight m16n8 accumulators. Shared rows are padded to 40 values, so that the eight rows a fragment load touches fall
+// into different banks. VEC: K, the row strides and the base addresses allow 16-byte loads.
+constexpr int HK = 32, HPAD = 40;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(128)
+gemm_heads_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w,
+                      __nv_bfloat16* __restrict__ out, int ldo, const __nv_bfloat16* __restrict__ gate, int ld_gate,
+                      float alpha, int M, int N, int K) {
+    __shared__ __align__(16) __nv_bfloat16 as[64][HPAD];
+    __shared__ __align__(16) __nv_bfloat16 ws[64][HPAD];
+    pdl_wait();
+    pdl_trigger();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, h = blockIdx.z;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const __nv_bfloat16* ah = a + (size_t)h * K;
+    const __nv_bfloat16* wh = w + (size_t)h * N * K;
+    float acc[8][4] = {};
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+    for (int k0 = 0; k0 < K; k0 += HK) {
+        if (VEC) {
+            // 64 rows x 4 chunks of 8 values per tile: two chunks a thread and tile
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = tid + 128 * j, row = c >> 2, kc = (c & 3) * 8, k = k0 + kc;
+                uint4 va = make_uint4(0, 0, 0, 0), vw = va;
+                if (k < K) {        // (K is a multiple of 8 here: a chunk is inside or outside as a whole)
+                    if (m0 + row < M) va = *reinterpret_cast<const uint4*>(ah + (size_t)(m0 + row) * lda + k);
+                    if (n0 + row < N) vw = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + row) * K + k);
+                }
+                *reinterpret_cast<uint4*>(&as[row][kc]) = va;
+                *reinterpret_cast<uint4*>(&ws[row][kc]) = vw;
+            }
+        } else {
+            for (int e = tid; e < 64 * HK; e += 128) {
+                const int row = e / HK, kc = e - row * HK, k = k0 + kc;
+                as[row][kc] = (m0 + row < M && k < K) ? ah[(size_t)(m0 + row) * lda + k] : zero;
+                ws[row][kc] = (n0 + row < N && k < K) ? wh[(size_t)(n0 + row) * K + k] : zero;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HK; kk += 16) {
+            const int r = warp * 16 + g;
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&as[r][kk + 2 * t]);
+            const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&as[r + 8][kk + 2 * t]);
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&as[r][kk + 2 * t + 8]);
+            const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&as[r + 8][kk + 2 * t + 8]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&ws[8 * j + g][kk + 2 * t]);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&ws[8 * j + g][kk + 2 * t + 8]);
+                mma_bf16_16816(acc[j], a0, a1, a2, a3, b0, b1);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int m = m0 + warp * 16 + g + 8 * half;
+        if (m >= M) continue;
+        float f = alpha;
+        if (gate != nullptr) {
+            const float gv = to_float(gate[(size_t)m * ld_gate + h]);
+            f = __fmul_rn(alpha, 1.f / (1.f + expf(-gv)));
+        }
+        __nv_bfloat16* dst = out + (size_t)m * ldo + (size_t)h * N;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + 8 * j + 2 * t;
+            if (n < N) dst[n] = __float2bfloat16_rn(__fmul_rn(acc[j][2 * half], f));
+            if (n + 1 < N) dst[n + 1] = __float2bfloat16_rn(__fmul_rn(acc[j][2 * half + 1], f));
+        }
+    }
+}
+
 }  // namespace
 
 JLLM_BOUNDS_READER(latent_attention)
@@ -124,12 +210,18 @@ JLLM_EXPORT int jllm_gemm_heads(const void* a, int dtype, int lda, const void* w
                  "gemm_heads: lda=%d ldo=%d for %d heads of K=%d, N=%d", lda, ldo, heads, K, N);
     if (M == 0) return JLLM_OK;
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
-    if (dtype == JLLM_F32)
+    static_assert(BM == 64 && BN == 64, "both kernels take 64 x 64 tiles");
+    if (dtype == JLLM_F32) {
         jllm_launch(gemm_heads_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (const float*)a, lda,
                     (const float*)w, (float*)out, ldo, (const float*)gate, ld_gate, alpha, M, N, K);
+        return jllm_check_launch("gemm_heads");
+    }
+    const bool vec = K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
+    if (vec)
+        jllm_launch(gemm_heads_mma_kernel<true>, grid, dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)a, lda,
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K);
     else
-        jllm_launch(gemm_heads_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT,
-                    (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo,
-                    (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K);
+        jllm_launch(gemm_heads_mma_kernel<false>, grid, dim3(128), 0, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)a, lda,
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ld_gate, alpha, M, N, K);
     return jllm_check_launch("gemm_heads");
 }

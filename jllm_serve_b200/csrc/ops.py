@@ -156,7 +156,7 @@ class _Signatures:
     jllm_bounds_error_latent_attention = [P]
     jllm_dynamic_tanh = [P, P, P, I, F, P, I, P, I, I, P]
     jllm_add_scaled = [P, P, F, ctypes.c_longlong, P]
-    jllm_gla_recurrent = [P, I, I, I, I, I, P, P, I, P, P, P, P, I, I, I, I, F, F, P]
+    jllm_gla_recurrent = [P, I, I, I, I, I, P, I, P, I, P, P, P, P, I, I, I, I, F, F, P]
     jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, P]
     jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
     jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, P]
@@ -209,12 +209,15 @@ def gla_recurrent(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg
                   value_dim, query_scale, temperature) -> None:
     """Gated linear attention over the segments of a step: per head S = diag(d) S + k v^T, o = S^T (query_scale q), d =
     sigmoid(decay_logits)^(1 / temperature). proj [rows, *]: q, k (heads x key_dim) and v (heads x value_dim) at the
-    given columns; decay_logits [rows, heads x key_dim] float32; state [slots, heads, key_dim, value_dim] float32, read
-    and written in place at `state_slots[segment]`; out [rows, heads x value_dim] float32."""
+    given columns; decay_logits [rows, heads x key_dim] float32, OVERWRITTEN with the decays (a launch of its own in
+    front of the recurrence); state [slots, heads, key_dim, value_dim] float32, read and written in place at
+    `state_slots[segment]`; out [rows, heads x value_dim] float32."""
+    global launch_count
+    launch_count += 1
     assert decay_logits.dtype == state.dtype == out.dtype == torch.float32 and proj.stride(1) == 1
     assert decay_logits.is_contiguous() and state.is_contiguous() and out.is_contiguous()
     _call("jllm_gla_recurrent", proj.data_ptr(), _DT[proj.dtype], proj.stride(0), q_off, k_off, v_off,
-          decay_logits.data_ptr(), state.data_ptr(), state.shape[0], seg_start.data_ptr(), seg_len.data_ptr(),
+          decay_logits.data_ptr(), decay_logits.shape[0], state.data_ptr(), state.shape[0], seg_start.data_ptr(), seg_len.data_ptr(),
           state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), heads, key_dim, value_dim, float(query_scale),
           float(temperature), _stream())
 

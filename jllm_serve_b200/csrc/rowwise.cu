@@ -160,6 +160,25 @@ dynamic_tanh_kernel(const float* __restrict__ x, VecRef w, VecRef b, float a, To
     const int r = blockIdx.x;
     const float* src = x + (size_t)(row_index ? row_index[r] : r) * dim;
     Tout* dst = out + (size_t)r * dim;
+    if ((dim & 3) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15u) == 0) {      // four values a thread at a time
+        for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            const float y0 = __fadd_rn(__fmul_rn(tanhf(__fmul_rn(a, v.x)), w[i]), b[i]);
+            const float y1 = __fadd_rn(__fmul_rn(tanhf(__fmul_rn(a, v.y)), w[i + 1]), b[i + 1]);
+            const float y2 = __fadd_rn(__fmul_rn(tanhf(__fmul_rn(a, v.z)), w[i + 2]), b[i + 2]);
+            const float y3 = __fadd_rn(__fmul_rn(tanhf(__fmul_rn(a, v.w)), w[i + 3]), b[i + 3]);
+            if constexpr (sizeof(Tout) == 4) {
+                *reinterpret_cast<float4*>(dst + i) = make_float4(y0, y1, y2, y3);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+                uint2 p;
+                p.x = *reinterpret_cast<uint32_t*>(&lo);
+                p.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst + i) = p;
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < dim; i += blockDim.x)
         dst[i] = from_float<Tout>(__fadd_rn(__fmul_rn(tanhf(__fmul_rn(a, src[i])), w[i]), b[i]));
 }
