@@ -28,14 +28,26 @@ route_experts_kernel(const T* __restrict__ h, int ld, const float* __restrict__ 
     for (int e = warp; e < experts; e += warps) {
         const float* wr = router + (size_t)e * dim;
         float acc = 0.f;
-        if (vec) {      // a lane takes four neighbouring values at a time; the order of the sum is fixed all the same
-            for (int i = lane * 4; i < dim; i += 128) {
-                const float4 a = *reinterpret_cast<const float4*>(hs + i), b = *reinterpret_cast<const float4*>(wr + i);
-                acc = fmaf(a.x, b.x, acc);
-                acc = fmaf(a.y, b.y, acc);
-                acc = fmaf(a.z, b.z, acc);
-                acc = fmaf(a.w, b.w, acc);
+        if (vec) {      // a lane takes four neighbouring values at a time, four such loads on their way together; the
+                        // order of the sum is fixed all the same
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int i0 = lane * 4; i0 < dim; i0 += 512) {
+                float4 b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    b[u] = i0 + 128 * u < dim ? *reinterpret_cast<const float4*>(wr + i0 + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (i0 + 128 * u < dim) {
+                        const float4 a = *reinterpret_cast<const float4*>(hs + i0 + 128 * u);
+                        part[u] = fmaf(a.x, b[u].x, part[u]);
+                        part[u] = fmaf(a.y, b[u].y, part[u]);
+                        part[u] = fmaf(a.z, b[u].z, part[u]);
+                        part[u] = fmaf(a.w, b[u].w, part[u]);
+                    }
+                }
             }
+            acc = (part[0] + part[1]) + (part[2] + part[3]);
         } else {
             for (int i = lane; i < dim; i += 32) acc = fmaf(hs[i], wr[i], acc);
         }

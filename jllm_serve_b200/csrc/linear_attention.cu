@@ -22,12 +22,13 @@ constexpr int TOKENS = 8;       // tokens staged at a time
 // d = sigmoid(z)^(1 / tau), in place over [rows, heads x dk] float32: log(sigmoid(z)) = min(z, 0) - log1p(exp(-|z|)),
 // times 1 / tau, exponentiated. Done once per step and element, in front of the recurrence (whose blocks would
 // otherwise each redo it for the columns they own).
-__global__ void gla_decay_kernel(float* __restrict__ z, float inv_tau, size_t total) {
+__global__ void gla_decay_kernel(float* __restrict__ z, float inv_tau, size_t total, int as_log) {
     pdl_wait();
     pdl_trigger();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const float v = z[i];
-        z[i] = expf(__fmul_rn(fminf(v, 0.f) - log1pf(expf(-fabsf(v))), inv_tau));
+        const float l = __fmul_rn(fminf(v, 0.f) - log1pf(expf(-fabsf(v))), inv_tau);
+        z[i] = as_log ? l : expf(l);        // (the chunked kernels want the logarithm: they add it up over a chunk)
     }
 }
 
@@ -220,6 +221,217 @@ int launch_recurrent_cols(const void* proj, int ld, int q_off, int k_off, int v_
 #undef JLLM_GLA_COLS
 }
 
+// ---- a prompt portion in chunks of 16 tokens ---------------------------------------------------------------------------
+// Within a chunk that starts with the state S0, with L_t the sum of the log-decays of the chunk's tokens up to t (per key
+// channel, <= 0) and L the sum over the whole chunk:
+//     o_t = (q_t * exp(L_t))^T S0  +  sum over s <= t of a_ts v_s,     a_ts = sum_i q_t[i] k_s[i] exp(L_t[i] - L_s[i])
+//     S   = diag(exp(L)) S0 + sum_s (k_s * exp(L - L_s)) v_s^T
+// Every exponent is a difference that is <= 0: nothing overflows however strong a decay is. The same multiply-adds as
+// token by token (plus the a_ts, a sixteenth more), but as small matrix products whose rows do not wait for one another:
+// `prepare` makes q * exp(L_t), k * exp(L - L_s), exp(L) and the a_ts for all chunks of all segments at once (nothing
+// there depends on the state), and `chunk` walks a segment's chunks in order, a block per (segment, head, 32 columns of
+// S) as in the kernel above. All of it float32; against the token-by-token kernel only the grouping of sums differs.
+constexpr int CHUNK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+gla_chunk_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, float* __restrict__ logd,
+                         const int* __restrict__ seg_start, const int* __restrict__ seg_len, float* __restrict__ qb,
+                         float* __restrict__ ke, float* __restrict__ scores, int heads, int dk, float q_scale) {
+    extern __shared__ __align__(16) float smem[];
+    const int dkp = dk + 1;                 // rows one float apart in the banks: threads of a warp read one column of many rows
+    float* L = smem;                        // [CHUNK][dkp]
+    float* Q = L + CHUNK * dkp;
+    float* K = Q + CHUNK * dkp;
+    pdl_wait();
+    pdl_trigger();
+    const int seg = blockIdx.x, t0 = blockIdx.y * CHUNK, h = blockIdx.z, n = seg_len[seg];
+    if (t0 >= n) return;
+    const int nt = min(CHUNK, n - t0);
+    const size_t row0 = (size_t)seg_start[seg] + t0, hd = (size_t)heads * dk;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+        float run = 0.f;
+        for (int t = 0; t < nt; ++t) {
+            run += logd[(row0 + t) * hd + (size_t)h * dk + i];
+            L[t * dkp + i] = run;
+            const T* p = proj + (row0 + t) * ld + (size_t)h * dk + i;
+            Q[t * dkp + i] = __fmul_rn(to_float(p[q_off]), q_scale);
+            K[t * dkp + i] = to_float(p[k_off]);
+        }
+        for (int t = 0; t < nt; ++t) {
+            qb[(row0 + t) * hd + (size_t)h * dk + i] = __fmul_rn(Q[t * dkp + i], expf(L[t * dkp + i]));
+            ke[(row0 + t) * hd + (size_t)h * dk + i] = __fmul_rn(K[t * dkp + i], expf(run - L[t * dkp + i]));
+        }
+        logd[row0 * hd + (size_t)h * dk + i] = expf(run);      // the chunk's whole decay, at its first row
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < CHUNK * CHUNK; p += blockDim.x) {
+        const int t = p / CHUNK, sx = p - t * CHUNK;
+        if (t >= nt) continue;
+        float acc = 0.f;
+        if (sx <= t)
+            for (int i = 0; i < dk; ++i)
+                acc = fmaf(__fmul_rn(Q[t * dkp + i], K[sx * dkp + i]), expf(L[t * dkp + i] - L[sx * dkp + i]), acc);
+        scores[((row0 + t) * heads + h) * CHUNK + sx] = acc;
+    }
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(512)
+gla_chunk_kernel(const T* __restrict__ proj, int ld, int v_off, const float* __restrict__ chunk_decay,
+                 const float* __restrict__ qb, const float* __restrict__ ke, const float* __restrict__ scores,
+                 float* __restrict__ state, const int* __restrict__ seg_start, const int* __restrict__ seg_len,
+                 const int* __restrict__ state_slots, float* __restrict__ o, int heads, int dk, int dv, int num_slots) {
+    extern __shared__ __align__(16) float smem[];
+    const int threads = blockDim.x, G = threads >> 5;
+    const int stage = 2 * CHUNK * dk + CHUNK * 32 + CHUNK * CHUNK + dk;     // qb, ke [CHUNK][dk], v [CHUNK][32], a, decay [dk]
+    float* part = smem + 2 * stage;                                         // [CHUNK][G][32]
+    pdl_wait();
+    pdl_trigger();
+    const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int tid = threadIdx.x, c = tid & 31, g = tid >> 5, j = c0 + c;
+    const int first = seg_start[seg], n = seg_len[seg], slot = state_slots[seg];
+    if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;
+    float* S = state + (((size_t)slot * heads + h) * dk) * dv;
+    const size_t hd = (size_t)heads * dk;
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = g * R + r;
+        s[r] = (i < dk && j < dv) ? S[(size_t)i * dv + j] : 0.f;
+    }
+    constexpr int EPT = CHUNK * R / 32;         // values of qb (and of ke) a thread fetches per chunk: CHUNK x dk / threads
+    float fq[EPT], fk[EPT], fv, fa, fd;
+    const int vt = tid >> 5, vpt_ok = tid < CHUNK * 32;      // (threads >= 32 x ... : v has CHUNK x 32 values)
+    auto fetch = [&](int t0) {
+        const int nt = min(CHUNK, n - t0);
+        const size_t base = (size_t)(first + t0);
+#pragma unroll
+        for (int u = 0; u < EPT; ++u) {
+            const int e = tid + u * threads, t = e / dk, i = e - t * dk;
+            fq[u] = fk[u] = 0.f;
+            if (e < CHUNK * dk && t < nt) {
+                fq[u] = qb[(base + t) * hd + (size_t)h * dk + i];
+                fk[u] = ke[(base + t) * hd + (size_t)h * dk + i];
+            }
+        }
+        fv = fa = 0.f;
+        fd = 1.f;
+        // v: one value a thread where the block has CHUNK x 32 threads or more, else several rounds (below)
+        if (vpt_ok && vt < nt && j < dv && threads >= CHUNK * 32)
+            fv = to_float(proj[(base + vt) * ld + v_off + (size_t)h * dv + j]);
+        if (tid < CHUNK * CHUNK && threads >= CHUNK * CHUNK) {
+            const int t = tid / CHUNK;
+            if (t < nt) fa = scores[((base + t) * heads + h) * CHUNK + (tid - t * CHUNK)];
+        }
+        if (tid < dk) fd = chunk_decay[base * hd + (size_t)h * dk + tid];
+    };
+    auto park = [&](int b, int t0) {
+        float* qs = smem + b * stage;
+        float* ks = qs + CHUNK * dk;
+        float* vs = ks + CHUNK * dk;
+        float* as = vs + CHUNK * 32;
+        float* dsm = as + CHUNK * CHUNK;
+#pragma unroll
+        for (int u = 0; u < EPT; ++u) {
+            const int e = tid + u * threads;
+            if (e < CHUNK * dk) {
+                qs[e] = fq[u];
+                ks[e] = fk[u];
+            }
+        }
+        if (threads >= CHUNK * 32) {
+            if (vpt_ok) vs[tid] = fv;
+        } else {        // a small block: it reads its values of v here, late (they are few)
+            const int nt = min(CHUNK, n - t0);
+            for (int e = tid; e < CHUNK * 32; e += threads) {
+                const int t = e >> 5, cc = e & 31;
+                vs[e] = (t < nt && c0 + cc < dv) ? to_float(proj[(size_t)(first + t0 + t) * ld + v_off + (size_t)h * dv + c0 + cc]) : 0.f;
+            }
+        }
+        if (threads >= CHUNK * CHUNK) {
+            if (tid < CHUNK * CHUNK) as[tid] = fa;
+        } else {
+            const int nt = min(CHUNK, n - t0);
+            for (int e = tid; e < CHUNK * CHUNK; e += threads) {
+                const int t = e / CHUNK;
+                as[e] = t < nt ? scores[(((size_t)(first + t0 + t)) * heads + h) * CHUNK + (e - t * CHUNK)] : 0.f;
+            }
+        }
+        for (int i = tid; i < dk; i += threads)
+            dsm[i] = i == tid ? fd : chunk_decay[(size_t)(first + t0) * hd + (size_t)h * dk + i];
+    };
+    if (n > 0) {
+        fetch(0);
+        park(0, 0);
+    }
+    __syncthreads();
+    for (int t0 = 0, b = 0; t0 < n; t0 += CHUNK, b ^= 1) {
+        const int nt = min(CHUNK, n - t0);
+        const bool more = t0 + CHUNK < n;
+        if (more) fetch(t0 + CHUNK);
+        const float* qs = smem + b * stage;
+        const float* ks = qs + CHUNK * dk;
+        const float* vs = ks + CHUNK * dk;
+        const float* as = vs + CHUNK * 32;
+        const float* dsm = as + CHUNK * CHUNK;
+        // what the state at the chunk's start gives every token, and the state at its end
+        float acc[CHUNK];
+#pragma unroll
+        for (int t = 0; t < CHUNK; ++t) acc[t] = 0.f;
+        float vreg[CHUNK];
+#pragma unroll
+        for (int t = 0; t < CHUNK; ++t) vreg[t] = vs[t * 32 + c];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = g * R + r;
+            if (i < dk) {
+                const float s0 = s[r];
+                float sn = __fmul_rn(dsm[i], s0);
+#pragma unroll
+                for (int t = 0; t < CHUNK; ++t) {
+                    acc[t] = fmaf(qs[t * dk + i], s0, acc[t]);
+                    sn = fmaf(ks[t * dk + i], vreg[t], sn);
+                }
+                s[r] = sn;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < CHUNK; ++t) part[(t * G + g) * 32 + c] = acc[t];
+        if (more) park(b ^ 1, t0 + CHUNK);
+        __syncthreads();
+        for (int e = tid; e < nt * 32; e += threads) {
+            const int t = e >> 5, cc = e & 31;
+            if (c0 + cc >= dv) continue;
+            float sum = 0.f;
+            for (int gg = 0; gg < G; ++gg) sum += part[(t * G + gg) * 32 + cc];
+            for (int sx = 0; sx <= t; ++sx) sum = fmaf(as[t * CHUNK + sx], vs[sx * 32 + cc], sum);
+            o[(size_t)(first + t0 + t) * ((size_t)heads * dv) + (size_t)h * dv + c0 + cc] = sum;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = g * R + r;
+        if (i < dk && j < dv) S[(size_t)i * dv + j] = s[r];
+    }
+}
+
+template <typename T, int R>
+int launch_chunked(const void* proj, int ld, int v_off, const float* chunk_decay, const float* qb, const float* ke,
+                   const float* scores, float* state, const int* seg_start, const int* seg_len, const int* state_slots,
+                   float* o, int segments, int heads, int dk, int dv, int num_slots, cudaStream_t stream) {
+    const int G = (dk + R - 1) / R;
+    const size_t smem = (size_t)(2 * (2 * CHUNK * dk + CHUNK * 32 + CHUNK * CHUNK + dk) + CHUNK * G * 32) * sizeof(float);
+    auto kernel = gla_chunk_kernel<T, R>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return jllm_fail(JLLM_CUDA_ERROR, "gla_chunk: %zu bytes of shared memory refused", smem);
+    jllm_launch(kernel, dim3(segments, heads, (dv + 31) / 32), dim3(G * 32), smem, stream, LAUNCH_DEPENDENT, (const T*)proj, ld,
+                v_off, chunk_decay, qb, ke, scores, state, seg_start, seg_len, state_slots, o, heads, dk, dv, num_slots);
+    return jllm_check_launch("gla_chunk");
+}
+
 // y[r, h, :] = o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * gain * silu(gate[r, h, :]) * scale; one warp per (row, head)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -263,24 +475,79 @@ JLLM_EXPORT int jllm_gla_recurrent(const void* proj, int dtype, int ld, int q_of
     {       // the decay logits become decays, in place
         const size_t total = (size_t)rows * heads * dk;
         const int blocks = (int)min((size_t)65535, (total + 255) / 256);
-        jllm_launch(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, z, inv_tau, total);
+        jllm_launch(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, z, inv_tau, total, 0);
         const int code = jllm_check_launch("gla_decay");
         if (code) return code;
     }
 #define JLLM_GLA(T, R)                                                                                                       \
     return launch_recurrent_cols<T, R>(proj, ld, q_off, k_off, v_off, z, state, seg_start, seg_len, state_slots, o, segments, \
                                        heads, dk, dv, q_scale, num_slots, stream)
+    // A step of single tokens is a chain of a few round trips to memory per block, whatever the block's size: many rows a
+    // thread make blocks small enough for several to share an SM. A prompt portion waits more than it computes: few rows
+    // a thread, so that more threads hide more of the waiting (at most 32 row groups of 32 columns: 1,024 threads).
+    // (Only the grouping of the partial sums of o differs between the two.)
+    const bool single = rows == segments;
     if (dtype == JLLM_F32) {
+        if (single) JLLM_GLA(float, 16);
         if (dk <= 128) JLLM_GLA(float, 4);
         if (dk <= 256) JLLM_GLA(float, 8);
         JLLM_GLA(float, 16);
     }
-    // few rows a thread: the kernel waits more than it computes, and more threads hide more of the waiting (at most
-    // 32 row groups of 32 columns: 1,024 threads)
+    if (single) JLLM_GLA(__nv_bfloat16, 16);
     if (dk <= 128) JLLM_GLA(__nv_bfloat16, 4);
     if (dk <= 256) JLLM_GLA(__nv_bfloat16, 8);
     JLLM_GLA(__nv_bfloat16, 16);
 #undef JLLM_GLA
+}
+
+// The same recurrence for steps with prompt portions, in chunks of 16 tokens (three launches: the log-decays in place
+// of z, the chunks' operands, the walk through the chunks). qb, ke [rows, heads x dk] and scores [rows, heads x 16] are
+// float32 scratch; `max_len`: the longest segment's rows.
+JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off, int k_off, int v_off, float* z, int rows,
+                                 float* qb, float* ke, float* scores, float* state, int num_slots, const int* seg_start,
+                                 const int* seg_len, const int* state_slots, float* o, int segments, int max_len, int heads,
+                                 int dk, int dv, float q_scale, float tau, cudaStream_t stream) {
+    JLLM_REQUIRE(segments >= 0 && rows >= 0 && heads > 0 && dk > 0 && dv > 0 && tau > 0.f && max_len >= 0,
+                 "gla_chunked: segments=%d heads=%d dk=%d dv=%d", segments, heads, dk, dv);
+    JLLM_REQUIRE(dk <= 512 && heads <= 65535 && (dv + 31) / 32 <= 65535 && (max_len + CHUNK - 1) / CHUNK <= 65535,
+                 "gla_chunked: dk=%d is above 512, or a segment of %d rows is too long", dk, max_len);
+    if (segments == 0 || rows == 0 || max_len == 0) return JLLM_OK;
+    {
+        const size_t total = (size_t)rows * heads * dk;
+        const int blocks = (int)min((size_t)65535, (total + 255) / 256);
+        jllm_launch(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, z, 1.f / tau, total, 1);
+        const int code = jllm_check_launch("gla_decay");
+        if (code) return code;
+    }
+    {
+        const size_t smem = (size_t)3 * CHUNK * (dk + 1) * sizeof(float);
+        const dim3 grid(segments, (max_len + CHUNK - 1) / CHUNK, heads);
+        if (dtype == JLLM_F32) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(gla_chunk_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            jllm_launch(gla_chunk_prepare_kernel<float>, grid, dim3(128), smem, stream, LAUNCH_DEPENDENT, (const float*)proj, ld,
+                        q_off, k_off, z, seg_start, seg_len, qb, ke, scores, heads, dk, q_scale);
+        } else {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(gla_chunk_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            jllm_launch(gla_chunk_prepare_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, LAUNCH_DEPENDENT,
+                        (const __nv_bfloat16*)proj, ld, q_off, k_off, z, seg_start, seg_len, qb, ke, scores, heads, dk, q_scale);
+        }
+        const int code = jllm_check_launch("gla_chunk_prepare");
+        if (code) return code;
+    }
+#define JLLM_GLA_CHUNK(T, R)                                                                                               \
+    return launch_chunked<T, R>(proj, ld, v_off, z, qb, ke, scores, state, seg_start, seg_len, state_slots, o, segments, heads, \
+                                dk, dv, num_slots, stream)
+    if (dtype == JLLM_F32) {
+        if (dk <= 32) JLLM_GLA_CHUNK(float, 4);
+        if (dk <= 128) JLLM_GLA_CHUNK(float, 8);
+        if (dk <= 256) JLLM_GLA_CHUNK(float, 16);
+        JLLM_GLA_CHUNK(float, 32);
+    }
+    if (dk <= 32) JLLM_GLA_CHUNK(__nv_bfloat16, 4);
+    if (dk <= 128) JLLM_GLA_CHUNK(__nv_bfloat16, 8);
+    if (dk <= 256) JLLM_GLA_CHUNK(__nv_bfloat16, 16);
+    JLLM_GLA_CHUNK(__nv_bfloat16, 32);
+#undef JLLM_GLA_CHUNK
 }
 
 JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype, int ld_gate, const void* gain,

@@ -157,6 +157,7 @@ class _Signatures:
     jllm_dynamic_tanh = [P, P, P, I, F, P, I, P, I, I, P]
     jllm_add_scaled = [P, P, F, ctypes.c_longlong, P]
     jllm_gla_recurrent = [P, I, I, I, I, I, P, I, P, I, P, P, P, P, I, I, I, I, F, F, P]
+    jllm_gla_chunked = [P, I, I, I, I, I, P, I, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, F, P]
     jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, P]
     jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
     jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, P]
@@ -220,6 +221,26 @@ def gla_recurrent(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg
           decay_logits.data_ptr(), decay_logits.shape[0], state.data_ptr(), state.shape[0], seg_start.data_ptr(), seg_len.data_ptr(),
           state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), heads, key_dim, value_dim, float(query_scale),
           float(temperature), _stream())
+
+
+GLA_CHUNK = 16      # tokens of a chunk of the chunked recurrence (CHUNK in linear_attention.cu)
+
+
+def gla_chunked(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg_len, state_slots, out, heads, key_dim,
+                value_dim, query_scale, temperature, max_len, qb, ke, scores) -> None:
+    """`gla_recurrent` for steps that hold prompt portions: the same recurrence in chunks of 16 tokens, whose multiply-adds
+    are small matrix products (float32 throughout; against the token-by-token kernel only the grouping of sums differs).
+    `max_len`: the longest segment's rows; qb, ke [rows, heads x key_dim] and scores [rows, heads x 16]: float32 scratch.
+    Three launches; decay_logits is overwritten."""
+    assert decay_logits.dtype == state.dtype == out.dtype == qb.dtype == ke.dtype == scores.dtype == torch.float32
+    assert proj.stride(1) == 1 and all(t.is_contiguous() for t in (decay_logits, state, out, qb, ke, scores))
+    assert qb.shape == ke.shape == decay_logits.shape and scores.shape == (decay_logits.shape[0], heads * GLA_CHUNK)
+    global launch_count
+    launch_count += 2
+    _call("jllm_gla_chunked", proj.data_ptr(), _DT[proj.dtype], proj.stride(0), q_off, k_off, v_off, decay_logits.data_ptr(),
+          decay_logits.shape[0], qb.data_ptr(), ke.data_ptr(), scores.data_ptr(), state.data_ptr(), state.shape[0],
+          seg_start.data_ptr(), seg_len.data_ptr(), state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), int(max_len),
+          heads, key_dim, value_dim, float(query_scale), float(temperature), _stream())
 
 
 def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim) -> None:

@@ -67,10 +67,12 @@ class LatentAttention(Mixer):
 
     def decode_bucket_cap(self, rows: int) -> int:
         s = self.spec
-        if not ops.attention_decode_fits(self.rt.dtype, s.heads, 1, s.rank):
+        heads = min(s.heads, 16)
+        if not ops.attention_decode_fits(self.rt.dtype, heads, 1, s.rank):
             return 1
         scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
-        return ops.decode_bucket_cap(rows, 1, s.heads, s.rank, s.window, scratch)
+        return max(ops.decode_bucket_cap(rows, 1, n, s.rank, s.window, scratch)
+                   for n in {heads, s.heads % 16 or heads})
 
     def forward(self, xb, x, batch, cache) -> None:
         s, rows = self.spec, xb.shape[0]
@@ -84,8 +86,13 @@ class LatentAttention(Mixer):
         ops.gemm_heads(proj[:, :H * dk], self.q_to_latent, q)
         att = self.rt.buffer("latent_attended", H * R)[:rows]
         scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
-        ops.attention(q, cache.keys, cache.values, att, batch, cache.group, H, 1, R, self.rt.page_size, s.window, s.scale,
-                      scratch)
+        # the decode kernel shares every key among at most 16 query heads: more heads go in groups of 16, each a launch
+        # over the same cached rows
+        per = 16 if H > 16 and ops.attention_decode_fits(q.dtype, 16, 1, R) else H
+        for h0 in range(0, H, per):
+            n = min(per, H - h0)
+            ops.attention(q[:, h0 * R:(h0 + n) * R], cache.keys, cache.values, att[:, h0 * R:(h0 + n) * R], batch,
+                          cache.group, n, 1, R, self.rt.page_size, s.window, s.scale, scratch)
         y = self.rt.buffer("latent_values", H * dv)[:rows]
         gate = proj[:, self.offsets[2]:self.offsets[2] + H] if s.gated else None
         ops.gemm_heads(att, self.latent_to_v, y, gate, self.residual_scale)

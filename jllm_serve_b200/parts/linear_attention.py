@@ -7,7 +7,8 @@ With h the normed rows, per head (dk query/key channels, dv value channels):
     x  += m Wo [ rmsnorm(o_t) * n  (per head, one gain n of dv values)  *  silu(Wg h_t) ]
 
 The state S [heads, dk, dv] is float32 and lives in the cache manager's state slots (zero when a request is opened), so a
-prompt may come in portions of any size and a decode step is the same kernel with one token per request. The decays,
+prompt may come in portions of any size. A decode step runs the recurrence token by token; a step with prompt portions
+runs it in chunks of sixteen tokens, as small matrix products (both float32: only the grouping of sums differs). The decays,
 their logarithms and the norm are computed in float32 in both precisions; q, k, v, the gate and the low-rank decay
 projection are one stacked product. The residual scale m is applied where the gated rows are written, in front of the
 output product, which adds into the residual stream itself.
@@ -80,8 +81,15 @@ class GatedLinearAttention(Mixer):
         z = self.rt.buffer("gla_decay_logits", H * dk, torch.float32)[:rows]
         self.decay.forward(proj[:, a_off:a_off + self.rank], z)
         o = self.rt.buffer("gla_out", H * dv, torch.float32)[:rows]
-        ops.gla_recurrent(proj, q_off, k_off, v_off, z, cache.state, batch.seg_start, batch.seg_len, batch.state_slots, o,
-                          H, dk, dv, s.query_scale, s.decay_temperature)
+        if batch.decode_only:
+            ops.gla_recurrent(proj, q_off, k_off, v_off, z, cache.state, batch.seg_start, batch.seg_len, batch.state_slots,
+                              o, H, dk, dv, s.query_scale, s.decay_temperature)
+        else:       # prompt portions (and the single rows beside them): sixteen tokens at a time
+            qb = self.rt.buffer("gla_chunk_queries", H * dk, torch.float32)[:rows]
+            ke = self.rt.buffer("gla_chunk_keys", H * dk, torch.float32)[:rows]
+            scores = self.rt.buffer("gla_chunk_scores", H * ops.GLA_CHUNK, torch.float32)[:rows]
+            ops.gla_chunked(proj, q_off, k_off, v_off, z, cache.state, batch.seg_start, batch.seg_len, batch.state_slots, o,
+                            H, dk, dv, s.query_scale, s.decay_temperature, batch.max_q_len, qb, ke, scores)
         y = self.rt.buffer("gla_gated", H * dv)[:rows]
         ops.gated_head_norm(o, proj[:, g_off:g_off + H * dv], self.gain, s.norm_eps, self.residual_scale, y, H, dv)
         self.out.forward(y, x, accumulate=True)

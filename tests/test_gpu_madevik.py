@@ -78,12 +78,14 @@ def plain_recurrence(q, k, v, z, tau, state):
 
 @pytest.mark.parametrize("heads, dk, dv", [(2, 16, 24), (1, 20, 12), (3, 64, 64), (1, 96, 33), (2, 128, 40), (1, 300, 8)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_linear_attention_recurrence_over_segments_slots_and_portions(heads, dk, dv, dtype):
+@pytest.mark.parametrize("chunked", [False, True])
+def test_linear_attention_recurrence_over_segments_slots_and_portions(heads, dk, dv, dtype, chunked):
     """Three requests in slots 2, 0 and 3 of a state storage with five: one of 37 tokens in portions of 1 + 20 + 2 + 14,
-    one of 9 tokens whole, one token by token; the others' slots keep the values they had."""
+    one of 9 tokens whole, one token by token; the others' slots keep the values they had. Token by token, and in
+    chunks (there with a temperature so low that some channels' decays over a chunk underflow: nothing may overflow)."""
     o_ = ops()
     g = torch.Generator().manual_seed(heads * 1000 + dk)
-    lengths, slots, tau, scale = {"a": 37, "b": 9, "c": 5}, {"a": 2, "b": 0, "c": 3}, 3.0, dk ** -0.5
+    lengths, slots, tau, scale = {"a": 37, "b": 9, "c": 5}, {"a": 2, "b": 0, "c": 3}, (0.05 if chunked else 3.0), dk ** -0.5
     width = heads * (2 * dk + dv) + 8
     data = {r: (torch.randn(n, width, generator=g).to(dtype), torch.randn(n, heads * dk, generator=g) * 3 + 2) for r, n in lengths.items()}
     state = torch.full((5, heads, dk, dv), 7.0, device=DEV)
@@ -98,9 +100,15 @@ def test_linear_attention_recurrence_over_segments_slots_and_portions(heads, dk,
         counts = [n for _, n in step]
         starts = [sum(counts[:i]) for i in range(len(counts))]
         out = torch.full((sum(counts), heads * dv), float("nan"), device=DEV)
-        o_.gla_recurrent(proj, q_off, k_off, v_off, z, state, torch.tensor(starts, dtype=torch.int32, device=DEV),
-                         torch.tensor(counts, dtype=torch.int32, device=DEV),
-                         torch.tensor([slots[r] for r, _ in step], dtype=torch.int32, device=DEV), out, heads, dk, dv, scale, tau)
+        tables = (torch.tensor(starts, dtype=torch.int32, device=DEV), torch.tensor(counts, dtype=torch.int32, device=DEV),
+                  torch.tensor([slots[r] for r, _ in step], dtype=torch.int32, device=DEV))
+        if chunked:
+            rows = sum(counts)
+            o_.gla_chunked(proj, q_off, k_off, v_off, z, state, *tables, out, heads, dk, dv, scale, tau, max(counts),
+                           torch.empty(rows, heads * dk, device=DEV), torch.empty(rows, heads * dk, device=DEV),
+                           torch.empty(rows, heads * o_.GLA_CHUNK, device=DEV))
+        else:
+            o_.gla_recurrent(proj, q_off, k_off, v_off, z, state, *tables, out, heads, dk, dv, scale, tau)
         for (r, n), s in zip(step, starts):
             got[r].append(out[s:s + n].cpu())
             fed[r] += n
