@@ -276,7 +276,7 @@ gla_chunk_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int k_of
     }
 }
 
-template <typename T, int R>
+template <typename T, int R, bool V4>
 __global__ void __launch_bounds__(512)
 gla_chunk_kernel(const T* __restrict__ proj, int ld, int v_off, const float* __restrict__ chunk_decay,
                  const float* __restrict__ qb, const float* __restrict__ ke, const float* __restrict__ scores,
@@ -382,18 +382,48 @@ gla_chunk_kernel(const T* __restrict__ proj, int ld, int v_off, const float* __r
         float vreg[CHUNK];
 #pragma unroll
         for (int t = 0; t < CHUNK; ++t) vreg[t] = vs[t * 32 + c];
+        if constexpr (V4) {     // dk a multiple of 4: four rows' values in one load (shared-memory instructions are what
+                                // bounds this loop: an SM issues one a clock)
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int i = g * R + r;
-            if (i < dk) {
-                const float s0 = s[r];
-                float sn = __fmul_rn(dsm[i], s0);
+            for (int r = 0; r < R; r += 4) {
+                const int i = g * R + r;
+                if (i < dk) {
+                    const float4 d4 = *reinterpret_cast<const float4*>(dsm + i);
+                    const float a0 = s[r], a1 = s[r + 1], a2 = s[r + 2], a3 = s[r + 3];
+                    float n0 = __fmul_rn(d4.x, a0), n1 = __fmul_rn(d4.y, a1), n2 = __fmul_rn(d4.z, a2), n3 = __fmul_rn(d4.w, a3);
 #pragma unroll
-                for (int t = 0; t < CHUNK; ++t) {
-                    acc[t] = fmaf(qs[t * dk + i], s0, acc[t]);
-                    sn = fmaf(ks[t * dk + i], vreg[t], sn);
+                    for (int t = 0; t < CHUNK; ++t) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(qs + t * dk + i);
+                        const float4 k4 = *reinterpret_cast<const float4*>(ks + t * dk + i);
+                        acc[t] = fmaf(q4.x, a0, acc[t]);
+                        acc[t] = fmaf(q4.y, a1, acc[t]);
+                        acc[t] = fmaf(q4.z, a2, acc[t]);
+                        acc[t] = fmaf(q4.w, a3, acc[t]);
+                        n0 = fmaf(k4.x, vreg[t], n0);
+                        n1 = fmaf(k4.y, vreg[t], n1);
+                        n2 = fmaf(k4.z, vreg[t], n2);
+                        n3 = fmaf(k4.w, vreg[t], n3);
+                    }
+                    s[r] = n0;
+                    s[r + 1] = n1;
+                    s[r + 2] = n2;
+                    s[r + 3] = n3;
                 }
-                s[r] = sn;
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int i = g * R + r;
+                if (i < dk) {
+                    const float s0 = s[r];
+                    float sn = __fmul_rn(dsm[i], s0);
+#pragma unroll
+                    for (int t = 0; t < CHUNK; ++t) {
+                        acc[t] = fmaf(qs[t * dk + i], s0, acc[t]);
+                        sn = fmaf(ks[t * dk + i], vreg[t], sn);
+                    }
+                    s[r] = sn;
+                }
             }
         }
 #pragma unroll
@@ -417,13 +447,13 @@ gla_chunk_kernel(const T* __restrict__ proj, int ld, int v_off, const float* __r
     }
 }
 
-template <typename T, int R>
+template <typename T, int R, bool V4>
 int launch_chunked(const void* proj, int ld, int v_off, const float* chunk_decay, const float* qb, const float* ke,
                    const float* scores, float* state, const int* seg_start, const int* seg_len, const int* state_slots,
                    float* o, int segments, int heads, int dk, int dv, int num_slots, cudaStream_t stream) {
     const int G = (dk + R - 1) / R;
     const size_t smem = (size_t)(2 * (2 * CHUNK * dk + CHUNK * 32 + CHUNK * CHUNK + dk) + CHUNK * G * 32) * sizeof(float);
-    auto kernel = gla_chunk_kernel<T, R>;
+    auto kernel = gla_chunk_kernel<T, R, V4>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return jllm_fail(JLLM_CUDA_ERROR, "gla_chunk: %zu bytes of shared memory refused", smem);
@@ -534,9 +564,11 @@ JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off,
         const int code = jllm_check_launch("gla_chunk_prepare");
         if (code) return code;
     }
-#define JLLM_GLA_CHUNK(T, R)                                                                                               \
-    return launch_chunked<T, R>(proj, ld, v_off, z, qb, ke, scores, state, seg_start, seg_len, state_slots, o, segments, heads, \
-                                dk, dv, num_slots, stream)
+#define JLLM_GLA_CHUNK(T, R)                                                                                                  \
+    return dk % 4 == 0 ? launch_chunked<T, R, true>(proj, ld, v_off, z, qb, ke, scores, state, seg_start, seg_len, state_slots, \
+                                                    o, segments, heads, dk, dv, num_slots, stream)                           \
+                       : launch_chunked<T, R, false>(proj, ld, v_off, z, qb, ke, scores, state, seg_start, seg_len,            \
+                                                     state_slots, o, segments, heads, dk, dv, num_slots, stream)
     if (dtype == JLLM_F32) {
         if (dk <= 32) JLLM_GLA_CHUNK(float, 4);
         if (dk <= 128) JLLM_GLA_CHUNK(float, 8);
