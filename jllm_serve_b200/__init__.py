@@ -1,4 +1,4 @@
-"""A B200-native inference engine for the Qwen3 dense architecture.
+"""A B200-native inference engine for the Qwen3 dense architecture and the Madevik design.
 
 Typed configuration and an architecture registry (`config`), weights by tensor name
 (`weights`), layers put together from parts (`parts`), a paged cache manager (`cache`),
