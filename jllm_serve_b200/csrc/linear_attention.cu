@@ -433,10 +433,27 @@ gla_chunk_kernel(const T* __restrict__ proj, int ld, int v_off, const float* __r
         for (int e = tid; e < nt * 32; e += threads) {
             const int t = e >> 5, cc = e & 31;
             if (c0 + cc >= dv) continue;
-            float sum = 0.f;
-            for (int gg = 0; gg < G; ++gg) sum += part[(t * G + gg) * 32 + cc];
-            for (int sx = 0; sx <= t; ++sx) sum = fmaf(as[t * CHUNK + sx], vs[sx * 32 + cc], sum);
-            o[(size_t)(first + t0 + t) * ((size_t)heads * dv) + (size_t)h * dv + c0 + cc] = sum;
+            // four running sums each way: one chain of dependent additions would be all latency (the order is fixed)
+            float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+            int gg = 0;
+            for (; gg + 4 <= G; gg += 4) {
+                p0 += part[(t * G + gg) * 32 + cc];
+                p1 += part[(t * G + gg + 1) * 32 + cc];
+                p2 += part[(t * G + gg + 2) * 32 + cc];
+                p3 += part[(t * G + gg + 3) * 32 + cc];
+            }
+            for (; gg < G; ++gg) p0 += part[(t * G + gg) * 32 + cc];
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            int sx = 0;
+            for (; sx + 4 <= t + 1; sx += 4) {
+                a0 = fmaf(as[t * CHUNK + sx], vs[sx * 32 + cc], a0);
+                a1 = fmaf(as[t * CHUNK + sx + 1], vs[(sx + 1) * 32 + cc], a1);
+                a2 = fmaf(as[t * CHUNK + sx + 2], vs[(sx + 2) * 32 + cc], a2);
+                a3 = fmaf(as[t * CHUNK + sx + 3], vs[(sx + 3) * 32 + cc], a3);
+            }
+            for (; sx <= t; ++sx) a0 = fmaf(as[t * CHUNK + sx], vs[sx * 32 + cc], a0);
+            o[(size_t)(first + t0 + t) * ((size_t)heads * dv) + (size_t)h * dv + c0 + cc] =
+                ((p0 + p1) + (p2 + p3)) + ((a0 + a1) + (a2 + a3));
         }
         __syncthreads();
     }
