@@ -110,17 +110,18 @@ def model_numbers(cfg: dict, layers: int) -> dict:
 
 
 def _moe(experts, top, ff):
-    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 2.0}}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 1.5}}
 
 
 def madevik_shape(width, heads, rank, experts, top, ff, runs, vocab=32768):
-    """Three linear-attention layers to one latent-attention layer, head size 128 throughout."""
+    """Every fourth layer, from the second on, attends over a cached latent, the others are linear attention; head size 128
+    throughout."""
     mlp = _moe(experts, top, ff)
-    gla = {"type": "gla", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 64}, "mlp": mlp}
+    gla = {"type": "gla", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64}, "mlp": mlp}
     latent = {"type": "latent_attention",
               "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": rank, "scale": 128 ** -0.5}, "mlp": mlp}
-    return {"architecture": "Madevik", "width": width, "vocab": vocab, "residual_mult": 0.5, "norm": {"eps": 1e-5},
-            "layers": [latent if i % 4 == 3 else gla for i in range(runs)]}
+    return {"architecture": "Madevik", "width": width, "vocab": vocab, "residual_mult": 0.7, "norm": {"eps": 1e-6},
+            "layers": [latent if i % 4 == 1 else gla for i in range(runs)]}
 
 
 # name -> (Madevik configuration, the Qwen3 dense shape of the same width, heads, layers and feed-forward weights)

@@ -26,7 +26,7 @@ def _latent(heads, dim, vdim, rank, scale, mlp, **more):
 
 
 # P: both mixers, each run twice (the second time with the first's tensors and a cache of its own)
-MADEVIK_P = {"architecture": "Madevik", "width": 64, "vocab": 211, "residual_mult": 0.5, "norm": {"eps": 1e-5}, "layers": [
+MADEVIK_P = {"architecture": "Madevik", "width": 64, "vocab": 211, "residual_mult": 0.6, "norm": {"eps": 2e-5}, "layers": [
     _gla(2, 16, 24, 8.0, 8, _moe(4, 2, 24, 1.5)),
     _latent(3, 16, 20, 64, 0.25, _moe(4, 2, 24, 1.5)),
     _gla(2, 16, 24, 8.0, 8, _moe(4, 2, 24, 1.5), weights_of=0),
@@ -40,10 +40,10 @@ MADEVIK_Q = {"architecture": "Madevik", "width": 72, "vocab": 130, "residual_mul
 # R: a latent of 128 values and more than 16 heads (the widths the tensor-core attention kernels take, and a group
 # the staged decode kernel does not), key widths of 64 and 96 in the linear attention, value width 33
 MADEVIK_R = {"architecture": "Madevik", "width": 128, "vocab": 300, "residual_mult": 0.25, "norm": {"eps": 1e-6}, "layers": [
-    _latent(20, 16, 16, 128, 0.2, _moe(8, 4, 32, 2.0)),
-    _gla(2, 64, 64, 16.0, 16, _moe(8, 4, 32, 2.0)),
+    _latent(20, 16, 16, 128, 0.2, _moe(6, 3, 32, 2.5)),
+    _gla(2, 64, 64, 12.0, 16, _moe(6, 3, 32, 2.5)),
     _gla(1, 96, 33, 4.0, 24, None),
-    _latent(4, 32, 48, 128, 0.15, _moe(8, 4, 32, 2.0))]}
+    _latent(4, 24, 40, 128, 0.15, _moe(6, 3, 32, 2.5))]}
 
 MADEVIK = {"P": MADEVIK_P, "Q": MADEVIK_Q, "R": MADEVIK_R}
 

@@ -16,10 +16,10 @@ def test_layers_that_borrow_weights_become_runs_of_one_layer():
     spec = parse_config(MADEVIK_P)
     assert model_type_of(MADEVIK_P) == "Madevik" and spec.core.dim == 64 and spec.core.vocab == 211
     assert len(spec.layers) == 2 and [r.layer for r in spec.schedule] == [0, 1, 0, 1]
-    assert [l.prefix for l in spec.layers] == ["l0.", "l1."] and all(l.residual_scale == 0.5 for l in spec.layers)
+    assert [l.prefix for l in spec.layers] == ["l0.", "l1."] and all(l.residual_scale == 0.6 for l in spec.layers)
     gla, latent = spec.layers[0].mixer, spec.layers[1].mixer
     assert (gla.heads, gla.key_dim, gla.value_dim, gla.decay_temperature, gla.decay_rank) == (2, 16, 24, 8.0, 8)
-    assert gla.query_scale == 0.25 and gla.norm_eps == 1e-5
+    assert gla.query_scale == 0.25 and gla.norm_eps == 2e-5
     assert (latent.heads, latent.key_dim, latent.value_dim, latent.rank, latent.scale) == (3, 16, 20, 64, 0.25)
     ff = spec.layers[0].feed_forward
     assert (ff.experts, ff.top, ff.hidden, ff.scale) == (4, 2, 24, 1.5) and spec.layers[0].norm.kind == "dynamic_tanh"
