@@ -15,7 +15,7 @@
 namespace {
 
 constexpr int THREADS = 128;
-constexpr int MAX_DIMS_PER_THREAD = 4;  // head_dim <= 512
+constexpr int MAX_DIMS_PER_THREAD = 8;  // head_dim <= 1024
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)

@@ -45,7 +45,19 @@ MADEVIK_R = {"architecture": "Madevik", "width": 128, "vocab": 300, "residual_mu
     _gla(1, 96, 33, 4.0, 24, None),
     _latent(4, 24, 40, 128, 0.15, _moe(6, 3, 32, 2.5))]}
 
-MADEVIK = {"P": MADEVIK_P, "Q": MADEVIK_Q, "R": MADEVIK_R}
+# S: linear attention only (no paged group at all: the model keeps states and nothing else), borrowed weights in a row
+MADEVIK_S = {"architecture": "Madevik", "width": 56, "vocab": 97, "residual_mult": 1.25, "norm": {"eps": 1e-6}, "layers": [
+    _gla(3, 12, 20, 4.0, 6, _moe(3, 2, 12, 1.0)),
+    _gla(3, 12, 20, 4.0, 6, _moe(3, 2, 12, 1.0), weights_of=0),
+    _gla(3, 12, 20, 4.0, 6, _moe(3, 2, 12, 1.0), weights_of=1)]}
+# T: latent attention only, three latents of different widths (three paged groups): 256 (the mma.sync flash kernel), 96
+# (the decode kernel's plain-load path, no flash kernel) and 520 (only the plain attention takes it)
+MADEVIK_T = {"architecture": "Madevik", "width": 96, "vocab": 150, "residual_mult": 0.8, "norm": {"eps": 1e-5}, "layers": [
+    _latent(3, 24, 16, 256, 0.2, None),
+    _latent(2, 16, 24, 96, 0.25, _moe(3, 2, 20, 1.2)),
+    _latent(17, 8, 8, 520, 0.35, None)]}
+
+MADEVIK = {"P": MADEVIK_P, "Q": MADEVIK_Q, "R": MADEVIK_R, "S": MADEVIK_S, "T": MADEVIK_T}
 
 
 def sharpen(tensors: dict, config: dict) -> dict:

@@ -247,6 +247,15 @@ def test_every_cut_of_the_same_requests_gives_the_plain_logits(name, dtype, way)
     run_trace(name, dtype, steps, {r: t for r, t in seqs.items() if r in used}, way)
 
 
+@pytest.mark.parametrize("way", ["prompt, then token by token", "mixed, slots and pages used again"])
+@pytest.mark.parametrize("name", ["S", "T"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_of_one_kind_of_mixer_only(name, dtype, way):
+    """States and no pages at all; pages in three groups of different widths and no state."""
+    seqs = sequences_for(name, (3, 70, 1, 141, 18), seed=31)
+    run_trace(name, dtype, WAYS[way](seqs), seqs, way)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_a_page_size_that_cuts_elsewhere(dtype):
     seqs = sequences_for("P", (420,), seed=5)
