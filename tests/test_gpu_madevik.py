@@ -317,6 +317,25 @@ def test_generation_with_preemption_in_a_small_pool_equals_plain():
         assert r.tokens == P.greedy_generate(cfg, w, p, 16), f"request {i}"
 
 
+def test_command_line_run_and_bench_on_a_madevik_model(tmp_path):
+    folder = madevik_folder("Q")
+    prompt = random_tokens(11, MADEVIK["Q"]["vocab"], 5)
+    cmd = [sys.executable, str(ROOT / "bin" / "jllm"), "run", "--model", str(folder), "--dtype", "fp32", "--temp", "0",
+           "--max-tokens", "7", "--ctx", "64", "--ignore-eos", "--tokens", ",".join(map(str, prompt))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    cfg, w = P.load_plain(folder)
+    assert [int(t) for t in proc.stdout.strip().split(",")] == P.greedy_generate(cfg, w, prompt, 7)
+    assert "11 prompt tok" in proc.stderr and "7 generated" in proc.stderr
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(MADEVIK["P"]))
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "jllm"), "bench", "--random-weights", "3", "--model-config",
+                           str(cfg_file), "--ctx", "256", "--bench.prompt-tokens", "50", "--bench.max-tokens", "8",
+                           "--bench.rounds", "2"], capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.startswith("prefill 50 tok in") and "decode 8 tok in" in proc.stdout
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_program_on_a_madevik_folder(dtype, tmp_path):
     seqs = sequences_for("P", (50, 7, 1, 90, 33), seed=30)
