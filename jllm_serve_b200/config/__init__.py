@@ -1,12 +1,14 @@
 """Typed configuration and the architecture registry."""
-from .specs import (ConfigError, Core, Decoder, DenseGluSpec, FeedForwardSpec, GatedLinearAttentionSpec, GqaAttentionSpec,
-                    LatentAttentionSpec, LayerNames, LayerRun, LayerSpec, ModelNames, MixerSpec, NormSpec, RopeScaling,
-                    RopeTableSpec, RoutedExpertsSpec)
+from .specs import (AttentionNames, ConfigError, Core, Decoder, DenseGluSpec, FeedForwardSpec, FixedDecayLinearAttentionSpec,
+                    GatedLinearAttentionSpec, GqaAttentionSpec, LatentAttentionSpec, LayerNames, LayerRun, LayerSpec, ModelNames,
+                    MixerSpec, NormSpec, ParallelMixersSpec, RopeScaling, RopeTableSpec, RoutedExpertsSpec)
 from .reader import ConfigReader
 from .registry import (architecture_entry, load_config, model_type_of, parse_config, register_architecture, supported_architectures,
                        unregister_architecture)
 from .families import DecoderDraft, parse_qwen3, parse_rope_scaling
 from .madevik import parse_madevik
+from .movivik import parse_movivik
 
 register_architecture("qwen3", parse_qwen3, replace=True)
 register_architecture("Madevik", parse_madevik, replace=True)
+register_architecture("Movivik", parse_movivik, replace=True)

@@ -37,11 +37,13 @@ class RopeScaling:
 
 @dataclass(frozen=True)
 class RopeTableSpec:
-    """One rotary table: `rotary_dim` values of each head are rotated, paired as (i, i + rotary_dim / 2)."""
+    """One rotary table: `rotary_dim` values of each head are rotated, paired as (i, i + rotary_dim / 2) ("half") or as
+    (2i, 2i + 1) ("interleaved"). The table itself (one angle per pair and position) is the same for both; the pairing
+    is what the mixer's kernel is told."""
     rotary_dim: int
     theta: float
     scaling: RopeScaling = RopeScaling()
-    pairing: str = "half"                  # half: (i, i + rotary_dim/2)
+    pairing: str = "half"                  # half: (i, i + rotary_dim/2); interleaved: (2i, 2i + 1)
     kind: str = field(default="rotary", init=False)   # which registered position encoding builds the table
 
     def __post_init__(self):
@@ -49,14 +51,15 @@ class RopeTableSpec:
             raise ConfigError(f"rotary_dim={self.rotary_dim} must be even and at least 2")
         if not self.theta > 0:
             raise ConfigError(f"rope_theta={self.theta} must be positive")
-        if self.pairing != "half":
-            raise ConfigError(f"rope pairing {self.pairing!r} is not built (built: half)")
+        if self.pairing not in ("half", "interleaved"):
+            raise ConfigError(f"rope pairing {self.pairing!r} is not built (built: half, interleaved)")
 
 
 @dataclass(frozen=True)
 class NormSpec:
     kind: str = "rmsnorm"                  # rmsnorm | dynamic_tanh (tanh(a x) * w + b: no statistics, eps unused)
     eps: float = 1e-6
+    gain_name: str = "weight"              # rmsnorm: the gain is the tensor <the norm's name> + gain_name ("": the name itself)
 
 
 @dataclass(frozen=True)
@@ -66,8 +69,27 @@ class MixerSpec:
 
 
 @dataclass(frozen=True)
+class AttentionNames:
+    """Checkpoint names of an attention's tensors, relative to the mixer's prefix."""
+    q: str = "q_proj.weight"
+    k: str = "k_proj.weight"
+    v: str = "v_proj.weight"
+    o: str = "o_proj.weight"
+    q_bias: str = "q_proj.bias"
+    k_bias: str = "k_proj.bias"
+    v_bias: str = "v_proj.bias"
+    o_bias: str = "o_proj.bias"
+    q_norm: str = "q_norm.weight"
+    k_norm: str = "k_norm.weight"
+    gate: str = "gate.weight"
+
+
+@dataclass(frozen=True)
 class GqaAttentionSpec(MixerSpec):
-    """Grouped-query causal attention over a paged cache (Attention.java:48-50,68-71)."""
+    """Grouped-query causal attention over a paged cache (Attention.java:48-50,68-71). Beyond the reference's: value heads
+    of another width than key heads (`value_dim`), rows that see only their own chunk of the sequence (`chunk`), a division
+    of every query and key head by its root mean square behind the rotation (`unit_qk`), and a sigmoid gate per head on the
+    attention's result, read from the mixer's input by one more projection (`gate`)."""
     kind: str = field(default="gqa_attention", init=False)
     heads: int = 0
     kv_heads: int = 0
@@ -79,6 +101,11 @@ class GqaAttentionSpec(MixerSpec):
     bias: bool = False                     # q, k, v biases
     out_bias: bool = False                 # o_proj bias
     scale: float = 0.0                     # multiplier of q . k
+    value_dim: int = 0                     # width of a value head; 0 = head_dim
+    chunk: int = 0                         # 0 = none; else position i sees j <= i only if i // chunk == j // chunk
+    unit_qk: bool = False                  # q and k over their root mean square (eps qk_norm_eps), after the rotation
+    gate: str = "none"                     # none | head_sigmoid: head h's result times sigmoid(Wg x)[h]
+    names: AttentionNames = AttentionNames()
 
     def __post_init__(self):
         if self.heads <= 0:
@@ -90,6 +117,16 @@ class GqaAttentionSpec(MixerSpec):
             raise ConfigError(f"head_dim must be positive, got {self.head_dim}")
         if self.window < 0:
             raise ConfigError(f"sliding_window={self.window} must not be negative")
+        if self.value_dim < 0 or self.chunk < 0:
+            raise ConfigError(f"attention: value_dim={self.value_dim} and chunk={self.chunk} must not be negative")
+        if self.chunk and self.window:
+            raise ConfigError("attention: a window and a chunk mask together are not built")
+        if self.gate not in ("none", "head_sigmoid"):
+            raise ConfigError(f"attention: gate {self.gate!r} is not built (built: none, head_sigmoid)")
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -114,6 +151,59 @@ class GatedLinearAttentionSpec(MixerSpec):
             raise ConfigError(f"gated linear attention: decay_rank={self.decay_rank} must be positive (or -1: as stored)")
         if not self.decay_temperature > 0:
             raise ConfigError(f"gated linear attention: tau={self.decay_temperature} must be positive")
+
+
+@dataclass(frozen=True)
+class FixedDecayLinearAttentionSpec(MixerSpec):
+    """Linear attention with one fixed decay per head and a recurrent state [heads, key_dim, value_dim] per request
+    ("lightning" attention): q, k, v = act(Wq h), act(Wk h), act(Wv h); S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T
+    (query_scale q_t); the heads' results are RMS-normed (all heads of a row together: `norm_over` "all", or "head" by
+    head) with a stored gain, gated by sigmoid(Wg h) (or silu) and projected."""
+    kind: str = field(default="fixed_decay_linear_attention", init=False)
+    heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    decays: Tuple[float, ...] = ()         # one per head, each in [0, 1]
+    activation: str = "silu"               # on q, k and v: silu | none
+    query_scale: float = 1.0
+    norm_eps: float = 1e-6
+    norm_over: str = "all"                 # all: one norm over heads x value_dim values (gain of that many); head: per head
+    gate: str = "sigmoid"                  # sigmoid | silu, of Wg h (heads x value_dim values)
+
+    def __post_init__(self):
+        for name in ("heads", "key_dim", "value_dim"):
+            if getattr(self, name) <= 0:
+                raise ConfigError(f"linear attention: {name}={getattr(self, name)} must be positive")
+        if len(self.decays) != self.heads:
+            raise ConfigError(f"linear attention: {len(self.decays)} decays for {self.heads} heads")
+        if any(not 0.0 <= d <= 1.0 for d in self.decays):
+            raise ConfigError(f"linear attention: every decay must lie in [0, 1], got {list(self.decays)}")
+        if self.activation not in ("silu", "none") or self.norm_over not in ("all", "head") or self.gate not in ("sigmoid", "silu"):
+            raise ConfigError(f"linear attention: activation={self.activation!r} norm_over={self.norm_over!r} "
+                              f"gate={self.gate!r} is not built")
+
+
+@dataclass(frozen=True)
+class ParallelMixersSpec(MixerSpec):
+    """Several mixers side by side on the same input; the result is `weight` times the sum of their results, each first
+    RMS-normed over the model width with a gain of its own (`out_norms[i]`, relative to the mixer's prefix). Branch i's
+    tensors lie under `prefixes[i]`; each keeps its own cache or state."""
+    kind: str = field(default="parallel_mixers", init=False)
+    branches: Tuple[MixerSpec, ...] = ()
+    prefixes: Tuple[str, ...] = ()
+    out_norms: Tuple[str, ...] = ()
+    norm_eps: float = 1e-6
+    weight: float = 0.5
+
+    def __post_init__(self):
+        if not 1 <= len(self.branches) <= 2:
+            raise ConfigError(f"parallel mixers: {len(self.branches)} branches (built: one or two)")
+        if not len(self.branches) == len(self.prefixes) == len(self.out_norms):
+            raise ConfigError("parallel mixers: every branch needs a prefix and the name of its norm")
+
+    @property
+    def rope_tables(self) -> tuple:
+        return tuple(getattr(b, "rope_table", -1) for b in self.branches)
 
 
 @dataclass(frozen=True)
@@ -147,13 +237,14 @@ class DenseGluSpec(FeedForwardSpec):
     """down(act(gate x) * (up x)) (Mlp.java:21)."""
     kind: str = field(default="dense_glu", init=False)
     hidden: int = 0
-    activation: str = "silu"
+    activation: str = "silu"               # silu | gelu_tanh (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))))
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")   # gate, up, down
 
     def __post_init__(self):
         if self.hidden <= 0:
             raise ConfigError(f"intermediate_size must be positive for a dense feed-forward, got {self.hidden}")
-        if self.activation != "silu":
-            raise ConfigError(f"unsupported hidden_act {self.activation!r}: only silu (SwiGLU) is built")
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ConfigError(f"unsupported hidden_act {self.activation!r}: silu (SwiGLU) and gelu_tanh are built")
 
 
 @dataclass(frozen=True)
@@ -186,6 +277,8 @@ class LayerNames:
     feed_forward: str = "mlp."
     mixer_norm: str = "input_layernorm."
     feed_forward_norm: str = "post_attention_layernorm."
+    mixer_post_norm: str = ""              # the `sandwich_norm` arrangement: the norm behind the mixer
+    feed_forward_post_norm: str = ""       # and the one behind the feed-forward
 
 
 @dataclass(frozen=True)
@@ -205,6 +298,7 @@ class LayerSpec:
     feed_forward: Optional[FeedForwardSpec]
     norm: NormSpec
     arrangement: str = "pre_norm"          # x += s * mixer(norm(x)); x += s * ffn(norm(x)), s = residual_scale
+                                           # sandwich_norm: x += post(mixer(norm(x))); x += post'(ffn(norm'(x)))
     names: LayerNames = LayerNames()
     residual_scale: float = 1.0
     prefix: Optional[str] = None           # the layer's checkpoint prefix where it is not ModelNames.layer.format(index)
@@ -262,9 +356,9 @@ class Decoder:
             if not getattr(t, "kind", ""):
                 raise ConfigError(f"position table {t!r} names no kind of position encoding")
         for spec in self.layers:
-            t = getattr(spec.mixer, "rope_table", -1)
-            if t >= len(self.rope_tables):
-                raise ConfigError(f"a layer names rope table {t} of {len(self.rope_tables)}")
+            for t in getattr(spec.mixer, "rope_tables", (getattr(spec.mixer, "rope_table", -1),)):
+                if t >= len(self.rope_tables):
+                    raise ConfigError(f"a layer names rope table {t} of {len(self.rope_tables)}")
 
     def with_schedule(self, schedule) -> "Decoder":
         runs = tuple(r if isinstance(r, LayerRun) else LayerRun(*r) for r in schedule)

@@ -140,6 +140,30 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- which keys a row sees ------------------------------------------------------------------------------
+// Every attention kernel takes one number, `window`, for the span of keys a row at position P sees besides P itself:
+//   0       every earlier key,
+//   w > 0   the last w keys (a sliding window),
+//   -c < 0  the keys of P's own chunk, chunks of c positions counted from position 0 of the sequence (a row never sees
+//           over a chunk's edge, wherever its prompt was cut).
+// The first visible key does not decrease with P, which is what the tile kernels' edge tests rely on.
+__host__ __device__ __forceinline__ int jllm_first_key(int P, int window) {
+    return window > 0 ? (P + 1 - window > 0 ? P + 1 - window : 0) : (window < 0 ? P - P % (-window) : 0);
+}
+
+// ---- the gate of a gated feed-forward: act(gate) * up -----------------------------------------------------
+// `kind` is what the products' launchers take as their `swiglu` argument: 0 no gating, 1 silu (z / (1 + exp(-z))),
+// 2 the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) = z / (1 + exp(-2 u)) with u the tanh's
+// argument. `fast`: the tensor-core epilogues, whose result is rounded to bfloat16 anyway, use the fast exponential.
+enum : int { GLU_NONE = 0, GLU_SILU = 1, GLU_GELU_TANH = 2 };
+template <bool FAST>
+__device__ __forceinline__ float glu_act(float z, int kind) {
+    float t = z;
+    if (kind == GLU_GELU_TANH) t = 1.5957691216057308f * __fmaf_rn(0.044715f * z, z * z, z);    // 2 sqrt(2 / pi) (z + c z^3)
+    if constexpr (FAST) return __fdividef(z, 1.f + __expf(-t));
+    return z / (1.f + expf(-t));
+}
+
 // A vector (gain, bias) whose stored type is known only at run time.
 struct VecRef {
     const void* p;

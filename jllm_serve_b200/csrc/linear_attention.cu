@@ -32,6 +32,43 @@ __global__ void gla_decay_kernel(float* __restrict__ z, float inv_tau, size_t to
     }
 }
 
+// Linear attention with ONE fixed decay per head (no decay projection; "lightning" attention) runs through the same
+// kernels: this pass fills the decay table with decay[h] for every key channel of head h (its logarithm for the chunked
+// form; a decay of 0 becomes a logarithm of -1e30, whose differences are 0 or below -1e30 and never NaN), and applies
+// the activation of such a mixer to its projections in place: q, k, v <- silu (activation 1). A block per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+fixed_decay_prepare_kernel(T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, float* __restrict__ z,
+                           const float* __restrict__ decay, int heads, int dk, int dv, int as_log, int activation) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t r = blockIdx.x;
+    float* zr = z + r * heads * dk;
+    for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
+        const float d = decay[i / dk];
+        zr[i] = as_log ? fmaxf(logf(d), -1e30f) : d;
+    }
+    if (!activation) return;
+    T* row = proj + r * ld;
+    for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
+        const float q = to_float(row[q_off + i]), k = to_float(row[k_off + i]);
+        row[q_off + i] = from_float<T>(q / (1.f + expf(-q)));
+        row[k_off + i] = from_float<T>(k / (1.f + expf(-k)));
+    }
+    for (int i = threadIdx.x; i < heads * dv; i += blockDim.x) {
+        const float v = to_float(row[v_off + i]);
+        row[v_off + i] = from_float<T>(v / (1.f + expf(-v)));
+    }
+}
+
+template <typename T>
+int launch_fixed_decay(void* proj, int ld, int q_off, int k_off, int v_off, float* z, const float* decay, int rows, int heads,
+                       int dk, int dv, int as_log, int activation, cudaStream_t stream) {
+    jllm_launch(fixed_decay_prepare_kernel<T>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, (T*)proj, ld, q_off, k_off,
+                v_off, z, decay, heads, dk, dv, as_log, activation);
+    return jllm_check_launch("fixed_decay_prepare");
+}
+
 template <typename T, int R, int CB, bool V4>
 __global__ void __launch_bounds__(1024)
 gla_recurrent_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
@@ -479,11 +516,12 @@ int launch_chunked(const void* proj, int ld, int v_off, const float* chunk_decay
     return jllm_check_launch("gla_chunk");
 }
 
-// y[r, h, :] = o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * gain * silu(gate[r, h, :]) * scale; one warp per (row, head)
+// y[r, h, :] = o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * gain * act(gate[r, h, :]) * scale, act = silu or (gate_kind 1)
+// sigmoid; one warp per (row, head). A norm over all heads together is the case heads = 1.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
-                       int rows, int heads, int dv, float eps, float scale) {
+                       int rows, int heads, int dv, float eps, float scale, int gate_kind) {
     pdl_wait();
     pdl_trigger();
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -498,8 +536,8 @@ gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, 
     T* dst = y + ((size_t)r * heads + h) * dv;
     for (int i = lane; i < dv; i += 32) {
         const float gv = to_float(gp[i]);
-        const float silu = gv / (1.f + expf(-gv));
-        dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[i]), silu), scale));
+        const float gated = (gate_kind == 1 ? 1.f : gv) / (1.f + expf(-gv));       // silu, or (kind 1) the logistic function
+        dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[i]), gated), scale));
     }
 }
 
@@ -513,13 +551,18 @@ JLLM_BOUNDS_READER(linear_attention)
 JLLM_EXPORT int jllm_gla_recurrent(const void* proj, int dtype, int ld, int q_off, int k_off, int v_off, float* z, int rows,
                                    float* state, int num_slots, const int* seg_start, const int* seg_len,
                                    const int* state_slots, float* o, int segments, int heads, int dk, int dv, float q_scale,
-                                   float tau, cudaStream_t stream) {
+                                   float tau, const float* head_decay, int activation, cudaStream_t stream) {
     JLLM_REQUIRE(segments >= 0 && rows >= 0 && heads > 0 && dk > 0 && dv > 0 && tau > 0.f,
                  "gla_recurrent: segments=%d heads=%d dk=%d dv=%d", segments, heads, dk, dv);
     JLLM_REQUIRE(dk <= 512 && heads <= 65535 && (dv + 7) / 8 <= 65535, "gla_recurrent: dk=%d is above 512", dk);
     if (segments == 0 || rows == 0) return JLLM_OK;
     const float inv_tau = 1.f / tau;
-    {       // the decay logits become decays, in place
+    if (head_decay) {     // one fixed decay per head: the table is filled (and q, k, v activated) instead
+        const int code = dtype == JLLM_F32
+            ? launch_fixed_decay<float>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 0, activation, stream)
+            : launch_fixed_decay<__nv_bfloat16>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 0, activation, stream);
+        if (code) return code;
+    } else {       // the decay logits become decays, in place
         const size_t total = (size_t)rows * heads * dk;
         const int blocks = (int)min((size_t)65535, (total + 255) / 256);
         jllm_launch(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, z, inv_tau, total, 0);
@@ -553,13 +596,19 @@ JLLM_EXPORT int jllm_gla_recurrent(const void* proj, int dtype, int ld, int q_of
 JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off, int k_off, int v_off, float* z, int rows,
                                  float* qb, float* ke, float* scores, float* state, int num_slots, const int* seg_start,
                                  const int* seg_len, const int* state_slots, float* o, int segments, int max_len, int heads,
-                                 int dk, int dv, float q_scale, float tau, cudaStream_t stream) {
+                                 int dk, int dv, float q_scale, float tau, const float* head_decay, int activation,
+                                 cudaStream_t stream) {
     JLLM_REQUIRE(segments >= 0 && rows >= 0 && heads > 0 && dk > 0 && dv > 0 && tau > 0.f && max_len >= 0,
                  "gla_chunked: segments=%d heads=%d dk=%d dv=%d", segments, heads, dk, dv);
     JLLM_REQUIRE(dk <= 512 && heads <= 65535 && (dv + 31) / 32 <= 65535 && (max_len + CHUNK - 1) / CHUNK <= 65535,
                  "gla_chunked: dk=%d is above 512, or a segment of %d rows is too long", dk, max_len);
     if (segments == 0 || rows == 0 || max_len == 0) return JLLM_OK;
-    {
+    if (head_decay) {
+        const int code = dtype == JLLM_F32
+            ? launch_fixed_decay<float>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 1, activation, stream)
+            : launch_fixed_decay<__nv_bfloat16>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 1, activation, stream);
+        if (code) return code;
+    } else {
         const size_t total = (size_t)rows * heads * dk;
         const int blocks = (int)min((size_t)65535, (total + 255) / 256);
         jllm_launch(gla_decay_kernel, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, z, 1.f / tau, total, 1);
@@ -601,7 +650,7 @@ JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off,
 
 JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype, int ld_gate, const void* gain,
                                      int gain_dtype, void* y, int rows, int heads, int dv, float eps, float scale,
-                                     cudaStream_t stream) {
+                                     int gate_kind, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && heads > 0 && dv > 0, "gated_head_norm: rows=%d heads=%d dv=%d", rows, heads, dv);
     if (rows == 0) return JLLM_OK;
     const VecRef g{gain, gain_dtype};
@@ -609,9 +658,9 @@ JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype
     const dim3 grid((unsigned)((warps + 7) / 8));
     if (dtype == JLLM_F32)
         jllm_launch(gated_head_norm_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o, (const float*)gate,
-                    ld_gate, g, (float*)y, rows, heads, dv, eps, scale);
+                    ld_gate, g, (float*)y, rows, heads, dv, eps, scale, gate_kind);
     else
         jllm_launch(gated_head_norm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
-                    (const __nv_bfloat16*)gate, ld_gate, g, (__nv_bfloat16*)y, rows, heads, dv, eps, scale);
+                    (const __nv_bfloat16*)gate, ld_gate, g, (__nv_bfloat16*)y, rows, heads, dv, eps, scale, gate_kind);
     return jllm_check_launch("gated_head_norm");
 }

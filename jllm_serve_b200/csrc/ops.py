@@ -131,7 +131,7 @@ class _Signatures:
     jllm_embed_rows = [P, P, I, P, I, I, I, P]
     jllm_feed_tokens = [P, P, I, I, P]
     jllm_rmsnorm = [P, P, I, P, I, P, I, I, F, P]
-    jllm_swiglu = [P, P, I, I, I, P]
+    jllm_swiglu = [P, P, I, I, I, I, P]
     jllm_qk_norm_rope_store = [P, I, P, P, I, I, F, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     jllm_gemm_plain = [P, I, I, P, I, P, I, P, I, I, I, I, I, I, P]
     jllm_gemm_small_m = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P]
@@ -142,7 +142,7 @@ class _Signatures:
     jllm_gemm_stream = [P, I, P, I, P, I, P, I, I, I, I, I, I, I, P, ctypes.c_longlong, I, P]
     jllm_gemm_tcgen05_error = []
     jllm_gemm_tcgen05_starve_next = []
-    jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P]
+    jllm_attention_plain = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
     jllm_attention_decode = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_decode_flat = [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     jllm_attention_prefill = [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P]
@@ -156,9 +156,12 @@ class _Signatures:
     jllm_bounds_error_latent_attention = [P]
     jllm_dynamic_tanh = [P, P, P, I, F, P, I, P, I, I, P]
     jllm_add_scaled = [P, P, F, ctypes.c_longlong, P]
-    jllm_gla_recurrent = [P, I, I, I, I, I, P, I, P, I, P, P, P, P, I, I, I, I, F, F, P]
-    jllm_gla_chunked = [P, I, I, I, I, I, P, I, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, F, P]
-    jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, P]
+    jllm_gla_recurrent = [P, I, I, I, I, I, P, I, P, I, P, P, P, P, I, I, I, I, F, F, P, I, P]
+    jllm_gla_chunked = [P, I, I, I, I, I, P, I, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, F, P, I, P]
+    jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, I, P]
+    jllm_head_prepare = [P, I, I, I, I, I, P, P, I, I, I, F, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
+    jllm_head_gate = [P, I, I, P, I, I, I, I, P]
+    jllm_norm_sum = [P, P, P, P, P, I, I, I, F, F, I, P]
     jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
     jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, P]
     jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, P]
@@ -207,12 +210,14 @@ def add_scaled(x: torch.Tensor, y: torch.Tensor, scale: float) -> None:
 
 
 def gla_recurrent(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg_len, state_slots, out, heads, key_dim,
-                  value_dim, query_scale, temperature) -> None:
+                  value_dim, query_scale, temperature, head_decay=None, activation: int = 0) -> None:
     """Gated linear attention over the segments of a step: per head S = diag(d) S + k v^T, o = S^T (query_scale q), d =
     sigmoid(decay_logits)^(1 / temperature). proj [rows, *]: q, k (heads x key_dim) and v (heads x value_dim) at the
     given columns; decay_logits [rows, heads x key_dim] float32, OVERWRITTEN with the decays (a launch of its own in
     front of the recurrence); state [slots, heads, key_dim, value_dim] float32, read and written in place at
-    `state_slots[segment]`; out [rows, heads x value_dim] float32."""
+    `state_slots[segment]`; out [rows, heads x value_dim] float32. With `head_decay` (float32 [heads]) every key channel of
+    head h decays by head_decay[h] instead: decay_logits is then scratch that the call fills, and `activation` 1 applies silu
+    to q, k and v in place in `proj` first."""
     global launch_count
     launch_count += 1
     assert decay_logits.dtype == state.dtype == out.dtype == torch.float32 and proj.stride(1) == 1
@@ -220,14 +225,21 @@ def gla_recurrent(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg
     _call("jllm_gla_recurrent", proj.data_ptr(), _DT[proj.dtype], proj.stride(0), q_off, k_off, v_off,
           decay_logits.data_ptr(), decay_logits.shape[0], state.data_ptr(), state.shape[0], seg_start.data_ptr(), seg_len.data_ptr(),
           state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), heads, key_dim, value_dim, float(query_scale),
-          float(temperature), _stream())
+          float(temperature), _head_decay(head_decay, heads), int(activation), _stream())
 
 
 GLA_CHUNK = 16      # tokens of a chunk of the chunked recurrence (CHUNK in linear_attention.cu)
 
 
+def _head_decay(head_decay, heads) -> int:
+    if head_decay is None:
+        return 0
+    assert head_decay.dtype == torch.float32 and head_decay.is_contiguous() and head_decay.numel() == heads
+    return head_decay.data_ptr()
+
+
 def gla_chunked(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg_len, state_slots, out, heads, key_dim,
-                value_dim, query_scale, temperature, max_len, qb, ke, scores) -> None:
+                value_dim, query_scale, temperature, max_len, qb, ke, scores, head_decay=None, activation: int = 0) -> None:
     """`gla_recurrent` for steps that hold prompt portions: the same recurrence in chunks of 16 tokens, whose multiply-adds
     are small matrix products (float32 throughout; against the token-by-token kernel only the grouping of sums differs).
     `max_len`: the longest segment's rows; qb, ke [rows, heads x key_dim] and scores [rows, heads x 16]: float32 scratch.
@@ -240,15 +252,18 @@ def gla_chunked(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg_l
     _call("jllm_gla_chunked", proj.data_ptr(), _DT[proj.dtype], proj.stride(0), q_off, k_off, v_off, decay_logits.data_ptr(),
           decay_logits.shape[0], qb.data_ptr(), ke.data_ptr(), scores.data_ptr(), state.data_ptr(), state.shape[0],
           seg_start.data_ptr(), seg_len.data_ptr(), state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), int(max_len),
-          heads, key_dim, value_dim, float(query_scale), float(temperature), _stream())
+          heads, key_dim, value_dim, float(query_scale), float(temperature), _head_decay(head_decay, heads), int(activation),
+          _stream())
 
 
-def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim) -> None:
-    """out[r, h] = rmsnorm(o[r, h]) * gain * silu(gate[r, h]) * scale over every head's value_dim values; o float32
-    [rows, heads x value_dim], gate a view [rows, heads x value_dim] with any row stride, out contiguous like gate's type."""
+def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim, gate_kind: str = "silu") -> None:
+    """out[r, h] = rmsnorm(o[r, h]) * gain * act(gate[r, h]) * scale over every head's value_dim values (act: "silu" or
+    "sigmoid"); o float32 [rows, heads x value_dim], gate a view [rows, heads x value_dim] with any row stride, out contiguous
+    like gate's type. heads = 1 norms all of a row together."""
     assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and gate.dtype == out.dtype
     _call("jllm_gated_head_norm", o.data_ptr(), gate.data_ptr(), _DT[gate.dtype], gate.stride(0), gain.data_ptr(),
-          _DT[gain.dtype], out.data_ptr(), o.shape[0], heads, value_dim, float(eps), float(scale), _stream())
+          _DT[gain.dtype], out.data_ptr(), o.shape[0], heads, value_dim, float(eps), float(scale),
+          {"silu": 0, "sigmoid": 1}[gate_kind], _stream())
 
 
 def latent_norm_store(src, gain, eps, slots, cache) -> None:
@@ -286,10 +301,51 @@ def scale_expert_hidden(hidden, weights, ff) -> None:
           weights.shape[1], int(ff), _stream())
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, hidden + j]."""
+GLU_KINDS = {"silu": 1, "gelu_tanh": 2}      # the gate's activation as the kernels number it (GLU_* in common.cuh)
+
+
+def glu_kind(activation) -> int:
+    """0 (no gating), or the kernels' number of a gated feed-forward's activation; True stands for silu. The products take
+    it as their `swiglu` argument: False, True, or the activation's name."""
+    if isinstance(activation, (bool, int)):
+        return int(activation)
+    return GLU_KINDS[activation] if activation else 0
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation="silu") -> None:
+    """out[r, j] = act(gate_up[r, j]) * gate_up[r, hidden + j], act = silu or gelu_tanh."""
     assert gate_up.dtype == out.dtype and gate_up.is_contiguous() and out.is_contiguous()
-    _call("jllm_swiglu", gate_up.data_ptr(), out.data_ptr(), _DT[out.dtype], out.shape[0], out.shape[1], _stream())
+    _call("jllm_swiglu", gate_up.data_ptr(), out.data_ptr(), _DT[out.dtype], out.shape[0], out.shape[1],
+          glu_kind(activation), _stream())
+
+
+def head_prepare(qkv, q_off, k_off, v_off, q_gain, k_gain, eps, cos, sin, rotary_dim, pairing, unit_norm, positions, slots,
+                 k_cache, v_cache, heads, kv_heads, key_dim, value_dim, page_size, write_kv=True) -> None:
+    """The general per-head preparation of an attention's rows: per query and key head an optional RMSNorm with gains,
+    the rotation of the first `rotary_dim` values (pairing "half": (i, i + rotary_dim / 2); "interleaved": (2i, 2i + 1)),
+    an optional division by the head's root mean square (`unit_norm`); queries go back in place, keys and values (which may
+    differ in width) into the cache rows `slots`. qkv [rows, stride] holds queries, keys and values at the given columns."""
+    use_norm = q_gain is not None
+    cache_dim = k_cache.shape[-1] if k_cache is not None else max(key_dim, value_dim)
+    _call("jllm_head_prepare", qkv.data_ptr(), _DT[qkv.dtype], qkv.stride(0), int(q_off), int(k_off), int(v_off), _p(q_gain),
+          _p(k_gain), _DT[q_gain.dtype] if use_norm else F32, int(use_norm), int(bool(unit_norm)), float(eps), _p(cos), _p(sin),
+          int(rotary_dim), {"half": 0, "interleaved": 1}[pairing], positions.data_ptr(), _p(slots), _p(k_cache), _p(v_cache),
+          int(write_kv), qkv.shape[0], heads, kv_heads, key_dim, value_dim, cache_dim, page_size, _stream())
+
+
+def head_gate(att, gate, heads, value_dim) -> None:
+    """att[r, h, :] *= sigmoid(gate[r, h]) in place; att [rows, heads x value_dim], gate a view [rows, heads]."""
+    assert att.dtype == gate.dtype and att.stride(1) == 1 and gate.stride(1) == 1 and att.shape[1] == heads * value_dim
+    _call("jllm_head_gate", att.data_ptr(), _DT[att.dtype], att.stride(0), gate.data_ptr(), gate.stride(0), att.shape[0],
+          heads, value_dim, _stream())
+
+
+def norm_sum(x, a, gain_a, eps, b=None, gain_b=None, scale: float = 1.0, accumulate: bool = True) -> None:
+    """x (+)= scale * (rmsnorm(a) * gain_a [+ rmsnorm(b) * gain_b]); x, a, b float32 [rows, dim], contiguous."""
+    assert x.dtype == a.dtype == torch.float32 and x.is_contiguous() and a.is_contiguous() and x.shape == a.shape
+    assert b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.shape == a.shape and gain_b.dtype == gain_a.dtype)
+    _call("jllm_norm_sum", x.data_ptr(), a.data_ptr(), gain_a.data_ptr(), _p(b), _p(gain_b), _DT[gain_a.dtype], x.shape[0],
+          x.shape[1], float(eps), float(scale), int(accumulate), _stream())
 
 
 def qk_norm_rope_store(qkv, q_gain, k_gain, eps, cos, sin, rotary_dim, positions, slots, k_cache, v_cache,
@@ -311,10 +367,14 @@ def gemm_plain(a, w, out, bias=None, accumulate=False) -> None:
 
 
 def attention_plain(q, q_stride, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads,
-                    head_dim, page_size, window, scale) -> None:
+                    head_dim, page_size, window, scale, value_dim: int = 0) -> None:
+    """`window`: 0 all earlier keys, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions.
+    `value_dim` (0: head_dim): the width of a value head where it differs from a key head's; the cache's rows are as
+    wide as k_cache's last dimension says."""
     _call("jllm_attention_plain", q.data_ptr(), q_stride, k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           out.stride(0), row_seg.data_ptr(), row_pos.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
-          rows, heads, kv_heads, head_dim, page_size, int(window), float(scale), _DT[q.dtype], _stream())
+          rows, heads, kv_heads, head_dim, int(value_dim or head_dim), k_cache.shape[-1], page_size, int(window),
+          float(scale), _DT[q.dtype], _stream())
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor, vocab: int | None = None) -> None:
@@ -457,7 +517,7 @@ def gemm_tcgen05(a, w, out, bias=None, accumulate=False, max_blocks: int = 0, sw
     ws = gemm_workspace(a.device, STREAM_WORKSPACE_FLOATS) if stream_mode == 1 else None
     _call("jllm_gemm_tcgen05", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.rows, w.cols, int(max_blocks), int(swiglu), _p(ws),
+          int(accumulate), a.shape[0], w.rows, w.cols, int(max_blocks), glu_kind(swiglu), _p(ws),
           ws.numel() if ws is not None else 0, int(stream_mode), int(tile_width), _stream())
 
 
@@ -471,7 +531,7 @@ def gemm_pair(a, w, out, bias=None, accumulate=False, swiglu=False, max_pairs: i
     ws = gemm_workspace((a.device, "pair"), PAIR_WORKSPACE_FLOATS) if stream_mode == 1 else None
     _call("jllm_gemm_pair", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.rows, w.cols, int(max_pairs), int(swiglu), _p(ws),
+          int(accumulate), a.shape[0], w.rows, w.cols, int(max_pairs), glu_kind(swiglu), _p(ws),
           ws.numel() if ws is not None else 0, int(stream_mode), _stream())
 
 
@@ -551,7 +611,7 @@ def gemm_stream(a, packed: PackedWeight, out, bias=None, accumulate=False, swigl
     ws = gemm_workspace((a.device, "stream"), SWAP_WORKSPACE_FLOATS)     # its own: it keeps counters of its own there
     _call("jllm_gemm_stream", a.data_ptr(), a.stride(0), packed.data.data_ptr(), packed.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0), int(accumulate),
-          a.shape[0], packed.rows, packed.cols, int(swiglu), ws.data_ptr(), ws.numel(), int(max_blocks), _stream())
+          a.shape[0], packed.rows, packed.cols, glu_kind(swiglu), ws.data_ptr(), ws.numel(), int(max_blocks), _stream())
 
 
 BOUNDS_FILES = ("attention_plain", "attention_decode", "attention_prefill", "attention_prefill_tc",
@@ -631,7 +691,7 @@ def gemm_small_m(a, w, out, bias=None, accumulate=False, swiglu=False) -> None:
     assert a.dtype == torch.bfloat16 and out.stride(-1) == 1 and a.shape[1] == w.cols
     _call("jllm_gemm_small_m", a.data_ptr(), a.stride(0), w.data.data_ptr(), w.k_blocks, _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
-          int(accumulate), a.shape[0], w.rows, w.cols, int(swiglu), _stream())
+          int(accumulate), a.shape[0], w.rows, w.cols, glu_kind(swiglu), _stream())
 
 
 def attention_decode_fits(dtype, heads, kv_heads, head_dim) -> bool:
@@ -707,7 +767,8 @@ def bucket_level(kv_bucket: int) -> int:
 
 
 def _windowed_bucket(kv_bucket: int, window: int) -> int:
-    return kv_bucket if window <= 0 else max(1, min(kv_bucket, window // 256))
+    """The bucket (keys in units of 256) that a row can see at most: a window's or a chunk's (-window) keys bound it."""
+    return kv_bucket if window == 0 else max(1, min(kv_bucket, abs(window) // 256))
 
 
 def decode_bucket_cap(rows, kv_heads, heads, head_dim, window, scratch, places: int = 0) -> int:
@@ -776,13 +837,18 @@ def _combine_launches(how, n, rows, kv_heads, head_dim) -> int:
 
 
 def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale,
-              scratch=None) -> None:
-    """Causal attention of every row of the batch over its own request's cached keys and values."""
-    if batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
+              scratch=None, value_dim: int = 0) -> None:
+    """Causal attention of every row of the batch over its own request's cached keys and values. `window`: 0 every
+    earlier key, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions (chunks counted from the
+    sequence's first position). `value_dim`: a value head's width where it is not `head_dim`; the tile kernels take heads
+    of one width only, so such a mixer runs on the plain kernel."""
+    one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim
+    one_width = one_width and window >= 0
+    if one_width and batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
         return _attention_decode_rows(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                       batch.rows, heads, kv_heads, head_dim, page_size, window, scale, batch.kv_bucket,
                                       scratch)
-    if q.dtype == torch.bfloat16 and attention_prefill_fits(head_dim):
+    if one_width and q.dtype == torch.bfloat16 and attention_prefill_fits(head_dim):
         # prompt portions through the flash kernel; the single rows riding beside them (the scheduler puts them
         # last) through the decode kernel, which shares every key among the query heads of a kv head
         ms, mr = batch.multi_segments, batch.multi_rows
@@ -799,7 +865,7 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
                                    batch.kv_bucket, scratch)
         return
     attention_plain(q, q.stride(0), k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
-                    batch.rows, heads, kv_heads, head_dim, page_size, window, scale)
+                    batch.rows, heads, kv_heads, head_dim, page_size, window, scale, value_dim)
 
 
 def attention_prefill_fits(head_dim) -> bool:

@@ -216,21 +216,21 @@ JLLM_EXPORT int jllm_add_scaled(float* x, const float* y, float scale, long long
 }
 
 // ---------------------------------------------------------------------------------------------------
-// SwiGLU: h[r, j] = silu(gate_up[r, j]) * gate_up[r, hidden + j],  silu(g) = g / (1 + exp(-g))
+// Gated hidden units: h[r, j] = act(gate_up[r, j]) * gate_up[r, hidden + j], act = silu (kind 1) or the tanh form of GELU (kind 2)
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ h, int hidden, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ h, int hidden, size_t total, int kind) {
     pdl_wait();
     pdl_trigger();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / hidden, j = i - r * hidden;
         const float g = to_float(gate_up[r * 2 * hidden + j]);
         const float u = to_float(gate_up[r * 2 * hidden + hidden + j]);
-        h[i] = from_float<T>(__fmul_rn(g / (1.f + expf(-g)), u));
+        h[i] = from_float<T>(__fmul_rn(glu_act<false>(g, kind), u));
     }
 }
 
-JLLM_EXPORT int jllm_swiglu(const void* gate_up, void* h, int dtype, int rows, int hidden, cudaStream_t stream) {
+JLLM_EXPORT int jllm_swiglu(const void* gate_up, void* h, int dtype, int rows, int hidden, int kind, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && hidden > 0, "swiglu: rows=%d hidden=%d", rows, hidden);
     if (rows == 0) return JLLM_OK;
     const size_t total = (size_t)rows * hidden;
@@ -238,10 +238,10 @@ JLLM_EXPORT int jllm_swiglu(const void* gate_up, void* h, int dtype, int rows, i
     const int blocks = (int)((total + 255) / 256 > most ? most : (total + 255) / 256);
     if (dtype == JLLM_F32)
         jllm_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (const float*)gate_up, (float*)h, hidden,
-                    total);
+                    total, kind);
     else
         jllm_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true, (const __nv_bfloat16*)gate_up,
-                    (__nv_bfloat16*)h, hidden, total);
+                    (__nv_bfloat16*)h, hidden, total, kind);
     return jllm_check_launch("swiglu");
 }
 
@@ -492,4 +492,195 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
             (__nv_bfloat16*)qkv, qg, kg, use_norm, eps, cos_t, sin_t, rotary_dim, positions, slots,
             (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, page_size, num_slots, row_stride);
     return jllm_check_launch("qk_norm_rope_store");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The general form of the per-head preparation, for mixers whose heads the kernel above does not take: key and value
+// heads of different widths, rotation of interleaved pairs, a unit norm behind the rotation. One warp per (row, head),
+// the head's values in the warp's slice of shared memory, in this order:
+//   1. (pre_norm) RMSNorm over the head with the gains q_gain / k_gain;
+//   2. rotation of the first rotary_dim values by the angles of the row's position, pair i = (i, i + rotary_dim / 2)
+//      ("half", pairing 0) or (2i, 2i + 1) ("interleaved", pairing 1);
+//   3. (post_norm) the head divided by its root mean square (no gain).
+// Queries go back in place; keys and values go into the paged cache, whose rows are cache_dim wide (keys fill the
+// first key_dim values of a row, values the first value_dim). qkv [rows, row_stride]: queries at column q_off (heads x
+// key_dim), keys at k_off (kv_heads x key_dim), values at v_off (kv_heads x value_dim).
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_prepare_kernel(T* __restrict__ qkv, int row_stride, int q_off, int k_off, int v_off, VecRef q_gain, VecRef k_gain,
+                    int pre_norm, int post_norm, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                    int rotary_dim, int pairing, const int* __restrict__ positions, const int* __restrict__ slots,
+                    T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads, int key_dim, int value_dim,
+                    int cache_dim, int page_size, int num_slots, int heads_total, long long items, int width) {
+    extern __shared__ float head_smem[];
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= items) return;
+    float* vec = head_smem + (size_t)(threadIdx.x >> 5) * width;
+    const int r = (int)(item / heads_total), h = (int)(item % heads_total);
+    const bool is_q = h < heads, is_k = !is_q && h < heads + kv_heads;
+    const int n = is_q || is_k ? key_dim : value_dim;
+    T* src = qkv + (size_t)r * row_stride +
+             (is_q ? q_off + (size_t)h * key_dim
+                   : is_k ? k_off + (size_t)(h - heads) * key_dim : v_off + (size_t)(h - heads - kv_heads) * value_dim);
+    for (int i = lane; i < n; i += 32) vec[i] = to_float(src[i]);
+    __syncwarp();
+    if (is_q || is_k) {
+        if (pre_norm) {
+            float ss = 0.f;
+            for (int i = lane; i < n; i += 32) ss = fmaf(vec[i], vec[i], ss);
+            const float s = rms_scale(warp_sum(ss), n, eps);
+            const VecRef g = is_q ? q_gain : k_gain;
+            for (int i = lane; i < n; i += 32) vec[i] = __fmul_rn(__fmul_rn(vec[i], s), g[i]);
+            __syncwarp();
+        }
+        if (rotary_dim > 0) {
+            const int half = rotary_dim >> 1;
+            const float* c = cos_t + (size_t)positions[r] * half;
+            const float* s = sin_t + (size_t)positions[r] * half;
+            for (int i = lane; i < half; i += 32) {
+                const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+                const float a = vec[ia], b = vec[ib];
+                vec[ia] = __fsub_rn(__fmul_rn(a, c[i]), __fmul_rn(b, s[i]));
+                vec[ib] = __fadd_rn(__fmul_rn(b, c[i]), __fmul_rn(a, s[i]));
+            }
+            __syncwarp();
+        }
+        if (post_norm) {
+            float ss = 0.f;
+            for (int i = lane; i < n; i += 32) ss = fmaf(vec[i], vec[i], ss);
+            const float s = rms_scale(warp_sum(ss), n, eps);
+            for (int i = lane; i < n; i += 32) vec[i] = __fmul_rn(vec[i], s);
+            __syncwarp();
+        }
+    }
+    T* dst = src;
+    if (!is_q) {
+        const int kvh = is_k ? h - heads : h - heads - kv_heads;
+        const int slot = slots[r];
+        if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;      // checked build: the write is dropped
+        const size_t page = slot / page_size, off = slot % page_size;
+        dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * cache_dim;
+    }
+    for (int i = lane; i < n; i += 32) dst[i] = from_float<T>(vec[i]);
+}
+
+JLLM_EXPORT int jllm_head_prepare(void* qkv, int dtype, int row_stride, int q_off, int k_off, int v_off, const void* q_gain,
+                                  const void* k_gain, int gain_dtype, int pre_norm, int post_norm, float eps,
+                                  const float* cos_t, const float* sin_t, int rotary_dim, int pairing, const int* positions,
+                                  const int* slots, void* k_cache, void* v_cache, int write_kv, int rows, int heads,
+                                  int kv_heads, int key_dim, int value_dim, int cache_dim, int page_size,
+                                  cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && heads > 0 && kv_heads > 0 && key_dim > 0 && value_dim > 0 && page_size > 0,
+                 "head_prepare: rows=%d heads=%d kv_heads=%d key_dim=%d value_dim=%d page_size=%d", rows, heads, kv_heads,
+                 key_dim, value_dim, page_size);
+    JLLM_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= key_dim && (pairing == 0 || pairing == 1),
+                 "head_prepare: rotary_dim=%d must be even and at most key_dim=%d; pairing=%d", rotary_dim, key_dim, pairing);
+    JLLM_REQUIRE(!write_kv || (cache_dim >= key_dim && cache_dim >= value_dim),
+                 "head_prepare: cache rows of %d values do not hold keys of %d and values of %d", cache_dim, key_dim, value_dim);
+    JLLM_REQUIRE(!pre_norm || (q_gain && k_gain), "head_prepare: a norm with gains needs both gains");
+    const int width = key_dim > value_dim ? key_dim : value_dim;
+    JLLM_REQUIRE(width <= 4096, "head_prepare: a head of %d values is above 4096", width);
+    if (rows == 0) return JLLM_OK;
+    const int num_slots = (int)min((long long)jllm_pool_pages() * page_size, 2147483647ll);   // 0 = not known
+    const int heads_total = write_kv ? heads + 2 * kv_heads : heads;
+    const long long items = (long long)rows * heads_total;
+    const dim3 grid((unsigned)((items + 7) / 8));
+    const size_t smem = (size_t)8 * width * sizeof(float);
+    const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    if (dtype == JLLM_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        jllm_launch(head_prepare_kernel<float>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (float*)qkv, row_stride, q_off,
+                    k_off, v_off, qg, kg, pre_norm, post_norm, eps, cos_t, sin_t, rotary_dim, pairing, positions, slots,
+                    (float*)k_cache, (float*)v_cache, heads, kv_heads, key_dim, value_dim, cache_dim, page_size, num_slots,
+                    heads_total, items, width);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        jllm_launch(head_prepare_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (__nv_bfloat16*)qkv,
+                    row_stride, q_off, k_off, v_off, qg, kg, pre_norm, post_norm, eps, cos_t, sin_t, rotary_dim, pairing,
+                    positions, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, key_dim, value_dim,
+                    cache_dim, page_size, num_slots, heads_total, items, width);
+    }
+    return jllm_check_launch("head_prepare");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// out[r, h, :] *= sigmoid(gate[r, h]): one gate value per row and head on the attention's result (heads x value_dim
+// values a row), the gate a column block of the mixer's stacked input product. In place.
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ att, int ld_att, const T* __restrict__ gate, int ld_gate, int heads,
+                                 int value_dim, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t per_row = (size_t)heads * value_dim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / per_row, c = i - r * per_row;
+        const float g = to_float(gate[r * ld_gate + c / value_dim]);
+        T* p = att + r * ld_att + c;
+        *p = from_float<T>(__fmul_rn(to_float(*p), 1.f / (1.f + expf(-g))));
+    }
+}
+
+JLLM_EXPORT int jllm_head_gate(void* att, int dtype, int ld_att, const void* gate, int ld_gate, int rows, int heads,
+                               int value_dim, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && heads > 0 && value_dim > 0, "head_gate: rows=%d heads=%d value_dim=%d", rows, heads, value_dim);
+    if (rows == 0) return JLLM_OK;
+    const size_t total = (size_t)rows * heads * value_dim;
+    const size_t most = (size_t)(jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1) * 16;
+    const int blocks = (int)((total + 255) / 256 > most ? most : (total + 255) / 256);
+    if (dtype == JLLM_F32)
+        jllm_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (float*)att, ld_att,
+                    (const float*)gate, ld_gate, heads, value_dim, total);
+    else
+        jllm_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, LAUNCH_DEPENDENT, (__nv_bfloat16*)att,
+                    ld_att, (const __nv_bfloat16*)gate, ld_gate, heads, value_dim, total);
+    return jllm_check_launch("head_gate");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Norms behind a part: x[r] += scale * (rmsnorm(a[r]) * gain_a  [+ rmsnorm(b[r]) * gain_b]), all float32 rows of
+// `dim` values. With one input it is the norm between a part's result and the residual sum; with two (and scale 1/2) the
+// mean of two normed results. `accumulate` 0 writes x instead of adding to it. A block per row; the row is read twice.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+norm_sum_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gain_a, const float* __restrict__ b, VecRef gain_b,
+                int dim, float eps, float scale, int accumulate) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const size_t row = (size_t)blockIdx.x * dim;
+    const float* pa = a + row;
+    const float* pb = b ? b + row : nullptr;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        sa = fmaf(pa[i], pa[i], sa);
+        if (pb) sb = fmaf(pb[i], pb[i], sb);
+    }
+    sa = block_sum(sa, scratch);
+    const float ra = rms_scale(sa, dim, eps);
+    float rb = 0.f;
+    if (pb) {
+        sb = block_sum(sb, scratch);
+        rb = rms_scale(sb, dim, eps);
+    }
+    float* px = x + row;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = __fmul_rn(__fmul_rn(pa[i], ra), gain_a[i]);
+        if (pb) v = __fadd_rn(v, __fmul_rn(__fmul_rn(pb[i], rb), gain_b[i]));
+        v = __fmul_rn(v, scale);
+        px[i] = accumulate ? __fadd_rn(px[i], v) : v;
+    }
+}
+
+JLLM_EXPORT int jllm_norm_sum(float* x, const float* a, const void* gain_a, const float* b, const void* gain_b, int gain_dtype,
+                              int rows, int dim, float eps, float scale, int accumulate, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0 && a && gain_a && (!b || gain_b), "norm_sum: rows=%d dim=%d", rows, dim);
+    if (rows == 0) return JLLM_OK;
+    jllm_launch(norm_sum_kernel, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, a, VecRef{gain_a, gain_dtype}, b,
+                VecRef{gain_b, gain_dtype}, dim, eps, scale, accumulate);
+    return jllm_check_launch("norm_sum");
 }

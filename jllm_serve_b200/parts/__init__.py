@@ -6,7 +6,8 @@ from .norm import DynamicTanh, RmsNorm
 from .rope import RotaryTable
 from .attention import GqaAttention
 from .mlp import DenseGlu
-from .linear_attention import GatedLinearAttention
+from .linear_attention import FixedDecayLinearAttention, GatedLinearAttention
+from .parallel import ParallelMixers
 from .latent_attention import LatentAttention
 from .experts import RoutedExperts
-from .block import PreNormBlock
+from .block import PreNormBlock, SandwichNormBlock

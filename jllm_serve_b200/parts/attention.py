@@ -8,6 +8,12 @@ Query head h reads kv head h // (heads / kv_heads) (cpu/KvCache.java:82,527). q,
 are one stacked [Q + 2 KV, dim] matrix, as the reference's fused `matmul3`.
 
 A run that reads another run's cache (`cache.writes == False`) projects queries only.
+
+What a spec may ask for beyond that: value heads of another width than key heads (a cache row is as wide as the wider of
+the two); rotation of interleaved pairs; q and k divided by their root mean square behind the rotation; a chunk mask (a row
+sees the earlier rows of its own chunk of the sequence only); a sigmoid gate per head, read from the mixer's input by rows
+that ride at the end of the stacked projection. These run through the general per-head kernel (`ops.head_prepare`) and
+the gate kernel; the attention itself is `ops.attention` for every form.
 """
 from __future__ import annotations
 
@@ -20,57 +26,90 @@ from .base import Mixer, register_mixer
 from .linear import Linear
 
 
+def _up8(n: int) -> int:
+    return -(-n // 8) * 8
+
+
 class GqaAttention(Mixer):
+    can_overwrite = True           # a block that norms the result before adding it asks for x = ... instead of x += ...
+
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, rope=None):
         self.spec, self.dim, self.rt, self.rope = spec, dim, runtime, rope
-        H, Hkv, hd = spec.heads, spec.kv_heads, spec.head_dim
-        self.q_width, self.kv_width = H * hd, Hkv * hd
-        names = ("q_proj", "k_proj", "v_proj")
-        w = [tensors.pop(prefix + n + ".weight") for n in names]
-        b = [tensors.pop(prefix + n + ".bias") for n in names] if spec.bias else None
+        self.overwrite = False
+        H, Hkv, hd, vd, names = spec.heads, spec.kv_heads, spec.head_dim, spec.v_dim, spec.names
+        self.q_width, self.k_width, self.v_width = H * hd, Hkv * hd, Hkv * vd
+        self.gated = spec.gate == "head_sigmoid"
+        # the classic form (one head width, pairs (i, i + half), nothing behind the rotation) runs on the fused kernels that
+        # were built for it; everything else on the general per-head kernel
+        self.classic = (vd == hd and not spec.unit_qk and (rope is None or rope.pairing == "half"))
+        w = [tensors.pop(prefix + n) for n in (names.q, names.k, names.v)]
+        b = [tensors.pop(prefix + n) for n in (names.q_bias, names.k_bias, names.v_bias)] if spec.bias else None
+        self.k_off, self.v_off = self.q_width, self.q_width + self.k_width
+        self.width = self.q_width + self.k_width + self.v_width
+        self.g_off = -1
+        if self.gated:
+            # the gate's rows ride at the end of the stacked product, from a multiple of 8 columns on
+            self.g_off = _up8(self.width)
+            g = tensors.pop(prefix + names.gate)
+            pad = self.g_off - self.width
+            if pad:
+                w.append(torch.zeros((pad, dim), dtype=g.dtype, device=g.device))
+            w.append(g)
+            if b:
+                b.append(torch.zeros((pad + H,), dtype=b[0].dtype, device=b[0].device))
+            self.width = self.g_off + H
         self.qkv = Linear(torch.cat(w, dim=0).contiguous(), torch.cat(b).contiguous() if b else None)
         self._q_only = None          # the query rows alone, made when a run first reads another run's cache
         del w, b
-        self.out = Linear(tensors.pop(prefix + "o_proj.weight"),
-                          tensors.pop(prefix + "o_proj.bias") if spec.out_bias else None)
-        self.q_gain = tensors.pop(prefix + "q_norm.weight") if spec.qk_norm else None
-        self.k_gain = tensors.pop(prefix + "k_norm.weight") if spec.qk_norm else None
+        self.out = Linear(tensors.pop(prefix + names.o), tensors.pop(prefix + names.o_bias) if spec.out_bias else None)
+        self.q_gain = tensors.pop(prefix + names.q_norm) if spec.qk_norm else None
+        self.k_gain = tensors.pop(prefix + names.k_norm) if spec.qk_norm else None
         if rope is not None and rope.rotary_dim > hd:
             raise ValueError(f"rotary_dim={rope.rotary_dim} exceeds head_dim={hd}")
+        # what the attention kernels are told about the keys a row sees: 0 all, w > 0 a window, -c < 0 chunks of c positions
+        self.span = -spec.chunk if spec.chunk else spec.window
 
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
-        H, Hkv, hd = spec.heads, spec.kv_heads, spec.head_dim
-        out = {prefix + "q_proj.weight": TensorWant((H * hd, dim)),
-               prefix + "k_proj.weight": TensorWant((Hkv * hd, dim)),
-               prefix + "v_proj.weight": TensorWant((Hkv * hd, dim)),
-               prefix + "o_proj.weight": TensorWant((dim, H * hd))}
+        H, Hkv, hd, vd, names = spec.heads, spec.kv_heads, spec.head_dim, spec.v_dim, spec.names
+        out = {prefix + names.q: TensorWant((H * hd, dim)),
+               prefix + names.k: TensorWant((Hkv * hd, dim)),
+               prefix + names.v: TensorWant((Hkv * vd, dim)),
+               prefix + names.o: TensorWant((dim, H * vd))}
         if spec.bias:
-            out.update({prefix + "q_proj.bias": TensorWant((H * hd,), "vector"),
-                        prefix + "k_proj.bias": TensorWant((Hkv * hd,), "vector"),
-                        prefix + "v_proj.bias": TensorWant((Hkv * hd,), "vector")})
+            out.update({prefix + names.q_bias: TensorWant((H * hd,), "vector"),
+                        prefix + names.k_bias: TensorWant((Hkv * hd,), "vector"),
+                        prefix + names.v_bias: TensorWant((Hkv * vd,), "vector")})
         if spec.out_bias:
-            out[prefix + "o_proj.bias"] = TensorWant((dim,), "vector")
+            out[prefix + names.o_bias] = TensorWant((dim,), "vector")
         if spec.qk_norm:
-            out[prefix + "q_norm.weight"] = TensorWant((hd,), "vector", init="gain")
-            out[prefix + "k_norm.weight"] = TensorWant((hd,), "vector", init="gain")
+            out[prefix + names.q_norm] = TensorWant((hd,), "vector", init="gain")
+            out[prefix + names.k_norm] = TensorWant((hd,), "vector", init="gain")
+        if spec.gate == "head_sigmoid":
+            out[prefix + names.gate] = TensorWant((H, dim))
         return out
 
     @classmethod
     def cache_need(cls, spec):
-        return PagedKeysValues(spec.kv_heads, spec.head_dim, spec.window)
+        # a cache row holds a key in its first head_dim values and a value in its first value_dim; a chunk mask gives no
+        # pages back early (the pool's books know windows only)
+        return PagedKeysValues(spec.kv_heads, max(spec.head_dim, spec.v_dim), spec.window)
+
+    def _tiles_fit(self) -> bool:
+        s = self.spec
+        return s.v_dim == s.head_dim and ops.attention_decode_fits(self.rt.dtype, s.heads, s.kv_heads, s.head_dim)
 
     def decode_bucket_cap(self, rows: int) -> int:
         s = self.spec
-        if not ops.attention_decode_fits(self.rt.dtype, s.heads, s.kv_heads, s.head_dim):
+        if not self._tiles_fit():
             return 1                   # the plain attention's launches do not depend on the context
         scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
-        return ops.decode_bucket_cap(rows, s.kv_heads, s.heads, s.head_dim, s.window, scratch)
+        return ops.decode_bucket_cap(rows, s.kv_heads, s.heads, s.head_dim, self.span, scratch)
 
     def forward(self, xb, x, batch, cache) -> None:
         s, rows = self.spec, xb.shape[0]
-        if cache.writes:
-            qkv = self.rt.buffer("qkv", self.q_width + 2 * self.kv_width)[:rows]
+        if cache.writes or not self.classic or self.gated:
+            qkv = self.rt.buffer("qkv", self.width)[:rows]
             self.qkv.forward(xb, qkv)
         else:
             qkv = self.rt.buffer("q_only", self.q_width)[:rows]
@@ -78,25 +117,34 @@ class GqaAttention(Mixer):
                 self._q_only = self.qkv.rows(0, self.q_width)
             self._q_only.forward(xb, qkv)
         rope = self.rope
-        att = self.rt.buffer("attention_out", self.q_width)[:rows]
+        att = self.rt.buffer("attention_out", s.heads * s.v_dim)[:rows]
         scratch = self.rt.buffer("attention_scratch", 2 << 20, torch.float32, rows=1)[0]
-        if (cache.writes and batch.decode_only and rope is not None and ops.attention_decode_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim)
+        if (self.classic and not self.gated and cache.writes and batch.decode_only and rope is not None
+                and ops.attention_decode_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim)
                 and ops.attention_decode_fresh_fits(qkv.dtype, s.heads, s.kv_heads, s.head_dim, rope.rotary_dim)):
             # a step of single rows: the attention kernel norms and rotates its own rows and writes their keys and values
             # (where that pays: it says whether it ran)
             if ops.attention_decode_fresh(qkv, self.q_gain, self.k_gain, s.qk_norm_eps, rope.cos, rope.sin, cache.keys,
                                           cache.values, att, batch.row_seg, batch.positions,
                                           batch.block_tables[cache.group], rows, s.heads, s.kv_heads, s.head_dim,
-                                          self.rt.page_size, s.window, s.scale, batch.kv_bucket, scratch):
-                return self.out.forward(att, x, accumulate=True)
-        ops.qk_norm_rope_store(qkv, self.q_gain, self.k_gain, s.qk_norm_eps,
-                               rope.cos if rope else None, rope.sin if rope else None,
-                               rope.rotary_dim if rope else 0, batch.positions,
-                               batch.slots[cache.group] if cache.writes else None, cache.keys, cache.values,
-                               s.heads, s.kv_heads, s.head_dim, self.rt.page_size, write_kv=cache.writes)
+                                          self.rt.page_size, self.span, s.scale, batch.kv_bucket, scratch):
+                return self.out.forward(att, x, accumulate=not self.overwrite)
+        slots = batch.slots[cache.group] if cache.writes else None
+        if self.classic:
+            ops.qk_norm_rope_store(qkv, self.q_gain, self.k_gain, s.qk_norm_eps,
+                                   rope.cos if rope else None, rope.sin if rope else None,
+                                   rope.rotary_dim if rope else 0, batch.positions, slots, cache.keys, cache.values,
+                                   s.heads, s.kv_heads, s.head_dim, self.rt.page_size, write_kv=cache.writes)
+        else:
+            ops.head_prepare(qkv, 0, self.k_off, self.v_off, self.q_gain, self.k_gain, s.qk_norm_eps,
+                             rope.cos if rope else None, rope.sin if rope else None, rope.rotary_dim if rope else 0,
+                             rope.pairing if rope else "half", s.unit_qk, batch.positions, slots, cache.keys, cache.values,
+                             s.heads, s.kv_heads, s.head_dim, s.v_dim, self.rt.page_size, write_kv=cache.writes)
         ops.attention(qkv, cache.keys, cache.values, att, batch, cache.group, s.heads, s.kv_heads, s.head_dim,
-                      self.rt.page_size, s.window, s.scale, scratch)
-        self.out.forward(att, x, accumulate=True)
+                      self.rt.page_size, self.span, s.scale, scratch, value_dim=s.v_dim)
+        if self.gated:
+            ops.head_gate(att, qkv[:, self.g_off:self.g_off + s.heads], s.heads, s.v_dim)
+        self.out.forward(att, x, accumulate=not self.overwrite)
 
 
 register_mixer("gqa_attention", GqaAttention, replace=True)

@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from ..weights.loader import TensorWant
 from .base import Block, part_class, register_block
 
 
@@ -27,6 +28,8 @@ class PreNormBlock(Block):
         mixer_cls = part_class("mixer", spec.mixer.kind)
         table = getattr(spec.mixer, "rope_table", -1)
         extra = {"rope": position_encodings[table]} if table is not None and table >= 0 and position_encodings else {}
+        if getattr(mixer_cls, "wants_position_encodings", False):      # a mixer of mixers: its branches pick their tables
+            extra = {"position_encodings": position_encodings}
         self.mixer = mixer_cls(spec.mixer, dim, tensors, prefix + names.mixer, runtime, **extra)
         self.ffn_norm = self.feed_forward = None
         if spec.feed_forward is not None:
@@ -92,3 +95,64 @@ class PreNormBlock(Block):
 
 
 register_block("pre_norm", PreNormBlock, replace=True)
+
+
+class SandwichNormBlock(PreNormBlock):
+    """A norm in front of each part and one behind it, before the residual sum:
+
+        x += post_norm(mixer(norm(x)));   x += post_norm'(feed_forward(norm'(x)))
+
+    The norms behind are RMS norms with gains of their own (`names.mixer_post_norm`, `names.feed_forward_post_norm`). A
+    part's result goes into a float32 buffer (the part is told to write instead of add: `overwrite`; one that cannot gets
+    the buffer zeroed), and one kernel norms it and adds it to the stream."""
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, position_encodings):
+        super().__init__(spec, dim, tensors, prefix, runtime, position_encodings)
+        if spec.norm.kind != "rmsnorm":
+            raise ValueError(f"the norm behind a part is an RMS norm; the layer's norm is {spec.norm.kind!r}")
+        if self.scale != 1.0:
+            raise ValueError("a residual scale together with norms behind the parts is not built")
+        names, gain = spec.names, getattr(spec.norm, "gain_name", "weight")
+        self.eps = float(spec.norm.eps)
+        self.mixer_post_gain = tensors[prefix + names.mixer_post_norm + gain]
+        self.ffn_post_gain = tensors[prefix + names.feed_forward_post_norm + gain] if self.feed_forward is not None else None
+        self._zero_first = set()
+        for part in (self.mixer, self.feed_forward):
+            if part is None:
+                continue
+            if getattr(part, "can_overwrite", False):
+                part.overwrite = True
+            else:
+                self._zero_first.add(id(part))
+
+    @classmethod
+    def wants(cls, spec, dim: int, prefix: str) -> dict:
+        out = super().wants(spec, dim, prefix)
+        names, gain = spec.names, getattr(spec.norm, "gain_name", "weight")
+        out[prefix + names.mixer_post_norm + gain] = TensorWant((dim,), "vector", init="gain")
+        if spec.feed_forward is not None:
+            out[prefix + names.feed_forward_post_norm + gain] = TensorWant((dim,), "vector", init="gain")
+        return out
+
+    def _result(self, part, rows):
+        y = self.rt.buffer("part_result", self.dim, torch.float32)[:rows]
+        if id(part) in self._zero_first:
+            y.zero_()
+        return y
+
+    def forward(self, x, batch, cache) -> None:
+        rows = x.shape[0]
+        xb = self.rt.buffer("normed", self.dim)[:rows]
+        self.mixer_norm.forward(x, xb)
+        y = self._result(self.mixer, rows)
+        self.mixer.forward(xb, y, batch, cache)
+        ops.norm_sum(x, y, self.mixer_post_gain, self.eps)
+        if self.feed_forward is None:
+            return
+        self.ffn_norm.forward(x, xb)
+        y = self._result(self.feed_forward, rows)
+        self.feed_forward.forward(xb, y, batch)
+        ops.norm_sum(x, y, self.ffn_post_gain, self.eps)
+
+
+register_block("sandwich_norm", SandwichNormBlock, replace=True)

@@ -96,3 +96,81 @@ class GatedLinearAttention(Mixer):
 
 
 register_mixer("gated_linear_attention", GatedLinearAttention, replace=True)
+
+
+class FixedDecayLinearAttention(Mixer):
+    """Linear attention with one fixed decay per head ("lightning" attention), through the kernels of the gated form:
+
+        q_t, k_t, v_t = act(Wq h_t), act(Wk h_t), act(Wv h_t)          (act = silu)
+        S_t = decay_head S_(t-1) + k_t v_t^T,   o_t = S_t^T (s q_t)      (S [heads, dk, dv] float32, in a state slot)
+        x  += Wo [ rmsnorm(o_t) * n  *  sigmoid(Wg h_t) ]               (the norm over all heads of a row together, or per head)
+
+    The decays are constants of the configuration, kept as float32 on the device; a pass in front of the recurrence fills
+    the decay table the kernels read (the decay for the token-by-token form, its logarithm for the chunked one) and applies
+    the activation to q, k and v where the stacked product left them. State, decays and the norm are float32 in both
+    precisions."""
+    can_overwrite = True
+
+    def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
+        self.spec, self.dim, self.rt = spec, dim, runtime
+        self.overwrite = False
+        H, dk, dv = spec.heads, spec.key_dim, spec.value_dim
+        parts = [tensors.pop(prefix + n) for n in ("q", "k", "v", "g")]
+        self.offsets, rows, at = [], [], 0
+        for w in parts:
+            self.offsets.append(at)
+            pad = _up8(w.shape[0]) - w.shape[0]
+            rows.append(w)
+            if pad:
+                rows.append(torch.zeros((pad, dim), dtype=w.dtype, device=w.device))
+            at += w.shape[0] + pad
+        self.width = at
+        self.inp = Linear(torch.cat(rows, dim=0).contiguous())
+        del parts, rows
+        self.out = Linear(tensors.pop(prefix + "o"))
+        self.gain = tensors.pop(prefix + "norm")
+        self.decay = torch.tensor(list(spec.decays), dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+    @classmethod
+    def wants(cls, spec, dim: int, prefix: str) -> dict:
+        H, dk, dv = spec.heads, spec.key_dim, spec.value_dim
+        return {prefix + "q": TensorWant((H * dk, dim)), prefix + "k": TensorWant((H * dk, dim)),
+                prefix + "v": TensorWant((H * dv, dim)), prefix + "g": TensorWant((H * dv, dim)),
+                prefix + "o": TensorWant((dim, H * dv)),
+                prefix + "norm": TensorWant((H * dv if spec.norm_over == "all" else dv,), "vector", init="gain")}
+
+    @classmethod
+    def cache_need(cls, spec):
+        return FixedState((spec.heads, spec.key_dim, spec.value_dim), "float32")
+
+    def decode_bucket_cap(self, rows: int) -> int:
+        return 1                       # nothing here looks at the context's length
+
+    def forward(self, xb, x, batch, cache) -> None:
+        s, rows = self.spec, xb.shape[0]
+        if not cache.writes or cache.state is None:
+            raise ops.KernelError("linear attention keeps its own state: a run cannot read another run's")
+        H, dk, dv = s.heads, s.key_dim, s.value_dim
+        q_off, k_off, v_off, g_off = self.offsets
+        act = 1 if s.activation == "silu" else 0
+        proj = self.rt.buffer("gla_proj", self.width)[:rows]
+        self.inp.forward(xb, proj)
+        z = self.rt.buffer("gla_decay_logits", H * dk, torch.float32)[:rows]
+        o = self.rt.buffer("gla_out", H * dv, torch.float32)[:rows]
+        if batch.decode_only:
+            ops.gla_recurrent(proj, q_off, k_off, v_off, z, cache.state, batch.seg_start, batch.seg_len, batch.state_slots,
+                              o, H, dk, dv, s.query_scale, 1.0, head_decay=self.decay, activation=act)
+        else:
+            qb = self.rt.buffer("gla_chunk_queries", H * dk, torch.float32)[:rows]
+            ke = self.rt.buffer("gla_chunk_keys", H * dk, torch.float32)[:rows]
+            scores = self.rt.buffer("gla_chunk_scores", H * ops.GLA_CHUNK, torch.float32)[:rows]
+            ops.gla_chunked(proj, q_off, k_off, v_off, z, cache.state, batch.seg_start, batch.seg_len, batch.state_slots, o,
+                            H, dk, dv, s.query_scale, 1.0, batch.max_q_len, qb, ke, scores, head_decay=self.decay,
+                            activation=act)
+        y = self.rt.buffer("gla_gated", H * dv)[:rows]
+        heads, width = (1, H * dv) if s.norm_over == "all" else (H, dv)
+        ops.gated_head_norm(o, proj[:, g_off:g_off + H * dv], self.gain, s.norm_eps, 1.0, y, heads, width, s.gate)
+        self.out.forward(y, x, accumulate=not self.overwrite)
+
+
+register_mixer("fixed_decay_linear_attention", FixedDecayLinearAttention, replace=True)

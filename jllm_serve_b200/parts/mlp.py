@@ -1,4 +1,4 @@
-"""The dense gated feed-forward: x += Wdown (silu(Wgate xb) * (Wup xb)).
+"""The dense gated feed-forward: x += Wdown (act(Wgate xb) * (Wup xb)), act = silu or the tanh form of GELU.
 
 Formula from the reference (src/main/java/org/robomiri/jllm/cpu/CpuBackend.java:661-669,
 silu at cpu/VectorKernels.java:637-639). As the reference's converter does
@@ -16,9 +16,14 @@ from .linear import Linear
 
 
 class DenseGlu(FeedForward):
+    can_overwrite = True           # a block that norms the result before adding it asks for x = ... instead of x += ...
+
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
         self.hidden, self.dim, self.rt = spec.hidden, dim, runtime
-        gate, up = tensors.pop(prefix + "gate_proj.weight"), tensors.pop(prefix + "up_proj.weight")
+        names = getattr(spec, "names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        self.activation = getattr(spec, "activation", "silu")      # silu | gelu_tanh: the kernels' epilogues take either
+        self.overwrite = False                                      # True: the result replaces x instead of being added to it
+        gate, up = tensors.pop(prefix + names[0]), tensors.pop(prefix + names[1])
         # bfloat16: blocks of 8 gate rows followed by their 8 up rows, so that the product's epilogue holds a
         # gate value and its up value together and applies SwiGLU itself (no [rows, 2 hidden] round trip)
         self.fused = gate.dtype == torch.bfloat16 and dim % 8 == 0 and spec.hidden % 8 == 0
@@ -29,24 +34,25 @@ class DenseGlu(FeedForward):
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous())
         del gate, up
-        self.down = Linear(tensors.pop(prefix + "down_proj.weight"))
+        self.down = Linear(tensors.pop(prefix + names[2]))
 
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
-        return {prefix + "gate_proj.weight": TensorWant((spec.hidden, dim)),
-                prefix + "up_proj.weight": TensorWant((spec.hidden, dim)),
-                prefix + "down_proj.weight": TensorWant((dim, spec.hidden))}
+        names = getattr(spec, "names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        return {prefix + names[0]: TensorWant((spec.hidden, dim)),
+                prefix + names[1]: TensorWant((spec.hidden, dim)),
+                prefix + names[2]: TensorWant((dim, spec.hidden))}
 
     def forward(self, xb, x, batch) -> None:
         rows = xb.shape[0]
         h = self.rt.buffer("ffn_hidden", self.hidden)[:rows]
         if self.fused:
-            self.gate_up.forward(xb, h, swiglu=True)
+            self.gate_up.forward(xb, h, swiglu=self.activation)
         else:
             gate_up = self.rt.buffer("gate_up", 2 * self.hidden)[:rows]
             self.gate_up.forward(xb, gate_up)
-            ops.swiglu(gate_up, h)
-        self.down.forward(h, x, accumulate=True)
+            ops.swiglu(gate_up, h, self.activation)
+        self.down.forward(h, x, accumulate=not self.overwrite)
 
 
 register_feed_forward("dense_glu", DenseGlu, replace=True)

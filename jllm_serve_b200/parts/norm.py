@@ -16,11 +16,11 @@ class RmsNorm(Norm):
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime):
         self.eps = float(spec.eps)
         self.dim = dim
-        self.gain = tensors[prefix + "weight"]
+        self.gain = tensors[prefix + getattr(spec, "gain_name", "weight")]
 
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
-        return {prefix + "weight": TensorWant((dim,), "vector", init="gain")}
+        return {prefix + getattr(spec, "gain_name", "weight"): TensorWant((dim,), "vector", init="gain")}
 
     def forward(self, x, out, row_index=None, rows=None):
         ops.rmsnorm(x, self.gain, self.eps, out, row_index, rows)

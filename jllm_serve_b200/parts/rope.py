@@ -32,11 +32,10 @@ def inverse_frequencies(spec, max_positions: int) -> torch.Tensor:
         low, high = correction_dim(sc.beta_fast), correction_dim(sc.beta_slow)
         low = max(math.floor(low) if sc.truncate else low, 0)
         high = min(math.ceil(high) if sc.truncate else high, d - 1)
-        if low == high:
-            high += 0.001
+        span = max(high - low, 0.001)       # (a ramp of no width is a step)
         for i in range(half):
             plain = 1.0 / math.pow(theta, (2.0 * i) / d)
-            ramp = min(max((i - low) / (high - low), 0), 1)
+            ramp = min(max((i - low) / span, 0), 1)
             f[i] = plain / sc.factor * ramp + plain * (1 - ramp)
     elif sc.kind != "none":
         raise ValueError(f"rope scaling {sc.kind!r} is not built")
