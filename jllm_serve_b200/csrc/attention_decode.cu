@@ -58,7 +58,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     pdl_wait();
     pdl_trigger();
     const int P = row_pos[r];
-    const int first = window > 0 ? max(0, P + 1 - window) : 0;
+    const int first = jllm_first_key(P, window);
     const int n_keys = P + 1 - first;
     // the block's share of the keys, in whole 16-key blocks
     const int blocks_total = (n_keys + 15) >> 4;

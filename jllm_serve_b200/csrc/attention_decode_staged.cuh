@@ -465,7 +465,7 @@ attention_decode_staged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     // (the wait for the kernel in front, which wrote the newest key and value of every row and the queries, is inside
     // `attend`, behind the look-ups and the first requests that do not depend on it)
     const int P = row_pos[r];
-    const int first = window > 0 ? max(0, P + 1 - window) : 0;
+    const int first = jllm_first_key(P, window);
     const int tiles_total = (P + 1 - first + TILE - 1) / TILE;
     const int tiles_per_split = (tiles_total + splits - 1) / splits;
     const int tile_lo = split * tiles_per_split, tile_hi = min(tiles_total, tile_lo + tiles_per_split);
@@ -500,7 +500,7 @@ __device__ __forceinline__ void flat_prefix(const int* __restrict__ row_pos, int
         const int r = base + lane;
         int incl = 0;
         if (r < rows) {
-            const int P = row_pos[r], first = window > 0 ? max(0, P + 1 - window) : 0;
+            const int P = row_pos[r], first = jllm_first_key(P, window);
             incl = (P + 1 - first + TILE - 1) / TILE;
         }
 #pragma unroll
@@ -544,7 +544,7 @@ attention_decode_flat_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, 
         const long long in_row = at - (long long)kv_heads * s_cum[r];
         const int kvh = (int)(in_row / tiles_r), tile_lo = (int)(in_row % tiles_r);
         const int n = (int)min((long long)(tiles_r - tile_lo), end - at);
-        const int P = row_pos[r], first = window > 0 ? max(0, P + 1 - window) : 0;
+        const int P = row_pos[r], first = jllm_first_key(P, window);
         const size_t slot = (size_t)r * kv_heads + kvh + blockIdx.x;
         // the blocks whose runs meet this pair follow one another (the host sees to it that no run is empty)
         const long long start = at - tile_lo;

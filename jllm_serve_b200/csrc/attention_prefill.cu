@@ -7,7 +7,8 @@
 // chunks, XOR-swizzled against bank conflicts, double-buffered so the next tile loads while this one is
 // used). Scores S = Q K^T and the output O += P V run on mma.sync.m16n8k16 with operands from ldmatrix;
 // the softmax is the online one in float32 (base 2), with the running maximum and sum per row in
-// registers. A row at position P sees keys [first, P], first = max(0, P + 1 - window) under a window.
+// registers. A row at position P sees keys [first, P], first = jllm_first_key(P, window): max(0, P + 1 - window) under a
+// window, the start of P's own chunk of -window positions under a chunk mask (window < 0).
 // Key tiles that no row of the query tile can see are skipped; positions that no row may see inside a
 // loaded tile are masked to -inf, and key rows past the last visible position are zero-filled instead of
 // read (their pages may belong to nobody).
@@ -94,7 +95,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     }
     cp_async_commit();
 
-    const int first_key = window > 0 ? max(0, pos0 + 1 - window) : 0;
+    const int first_key = jllm_first_key(pos0, window);     // (the tile's first row sees the earliest key)
     const int kt_lo = first_key / BKV, kt_hi = pos_last / BKV;  // inclusive range of key tiles
     const size_t page_stride = (size_t)kv_heads * page_size * HD;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
@@ -135,9 +136,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     // positions of this thread's two rows (rows past the end act like the last real row and are not stored)
-    int pos_r[2];
+    int pos_r[2], first_r[2];      // a row's position and the first key it sees (window or chunk)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) pos_r[h] = pos0 + min(warp * 16 + g + 8 * h, rows_here - 1);
+    for (int h = 0; h < 2; ++h) {
+        pos_r[h] = pos0 + min(warp * 16 + g + 8 * h, rows_here - 1);
+        first_r[h] = jllm_first_key(pos_r[h], window);
+    }
 
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int buf = (kt - kt_lo) & 1;
@@ -174,7 +178,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             // a tile that every row of this warp sees whole (all keys at or before the warp's first position and
             // inside every row's window) needs no mask: true for all but the tiles on the diagonal and the window's edge
             const int warp_first = pos0 + min(warp * 16, rows_here - 1), warp_last = pos0 + min(warp * 16 + 15, rows_here - 1);
-            const bool whole = key0 + BKV - 1 <= warp_first && (window <= 0 || key0 >= warp_last + 1 - window);
+            const bool whole = key0 + BKV - 1 <= warp_first && key0 >= jllm_first_key(warp_last, window);
             if (whole) {
     #pragma unroll
                 for (int j = 0; j < BKV / 8; ++j)
@@ -189,7 +193,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int key = key0 + j * 8 + 2 * t + (i & 1), P = pos_r[i >> 1];
-                        const bool vis = key <= P && (window <= 0 || key >= P + 1 - window);
+                        const bool vis = key <= P && key >= first_r[i >> 1];
                         s[j][i] = vis ? s[j][i] * scale_log2 : -INFINITY;
                         mx[i >> 1] = fmaxf(mx[i >> 1], s[j][i]);
                     }

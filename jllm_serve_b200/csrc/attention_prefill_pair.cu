@@ -76,7 +76,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
     const int rows_here = min(2 * BQ, n_rows - q0);                    // rows of both tiles
     const int row0 = seg_start[seg] + q0;
     const int pos0 = seg_kv_len[seg] - n_rows + q0, pos_last = pos0 + rows_here - 1;
-    const int first_key = window > 0 ? max(0, pos0 + 1 - window) : 0;
+    const int first_key = jllm_first_key(pos0, window);     // (the tile's first row sees the earliest key)
     const int kt_lo = first_key / BKV;
     // key tiles that each query tile walks (tile B none if the pair has at most 128 rows)
     const int rows_x[2] = {min(BQ, rows_here), max(0, rows_here - BQ)};
@@ -225,7 +225,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
             const uint32_t s_addr = lane_addr + x * 128, o_addr = lane_addr + 256 + x * 128;
             const int P = pos0 + x * BQ + min(r, rows_x[x] - 1);   // rows past the end copy the last row, and are not stored
-            const int lo = window > 0 ? max(0, P + 1 - window) : 0;
+            const int lo = jllm_first_key(P, window);              // the first key this row sees (window or chunk)
             const int pos0_x = pos0 + x * BQ;
             float m = -INFINITY, l = 0.f;
             bool ok = true;

@@ -68,7 +68,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int rows_here = min(BQ, n_rows - q0);
     const int row0 = seg_start[seg] + q0;
     const int pos0 = seg_kv_len[seg] - n_rows + q0, pos_last = pos0 + rows_here - 1;
-    const int first_key = window > 0 ? max(0, pos0 + 1 - window) : 0;
+    const int first_key = jllm_first_key(pos0, window);     // (the tile's first row sees the earliest key)
     const int kt_lo = first_key / BKV, kt_hi = pos_last / BKV, n_tiles = kt_hi - kt_lo + 1;
     const int* table = block_tables + (size_t)seg * table_stride;
 
@@ -204,14 +204,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int quad = warp & 3, r = quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         const int P = pos0 + min(r, rows_here - 1);            // rows past the end copy the last row, and are not stored
-        const int lo = window > 0 ? max(0, P + 1 - window) : 0;
+        const int lo = jllm_first_key(P, window);              // the first key this row sees (window or chunk)
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int b = j & 1, key0 = (kt_lo + j) * BKV;
             if (!mbar_wait(bar(S_FULL + b), (j >> 1) & 1u, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
-            const bool masked = key0 + BKV - 1 > pos0 || key0 < lo || (window > 0 && key0 < pos_last + 1 - window);
+            const bool masked = key0 + BKV - 1 > pos0 || key0 < lo || key0 < jllm_first_key(pos_last, window);
             // the row of S: four loads in flight, one wait
             uint32_t v[4][32];
 #pragma unroll

@@ -843,7 +843,6 @@ def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim,
     sequence's first position). `value_dim`: a value head's width where it is not `head_dim`; the tile kernels take heads
     of one width only, so such a mixer runs on the plain kernel."""
     one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim
-    one_width = one_width and window >= 0
     if one_width and batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):
         return _attention_decode_rows(q, k_cache, v_cache, out, batch.row_seg, batch.positions, batch.block_tables[group],
                                       batch.rows, heads, kv_heads, head_dim, page_size, window, scale, batch.kv_bucket,

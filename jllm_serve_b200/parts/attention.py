@@ -55,9 +55,13 @@ class GqaAttention(Mixer):
             if pad:
                 w.append(torch.zeros((pad, dim), dtype=g.dtype, device=g.device))
             w.append(g)
+            # (and the row's width stays a multiple of 8 values: the tile kernels read queries by 16-byte pieces)
+            tail = _up8(H) - H
+            if tail:
+                w.append(torch.zeros((tail, dim), dtype=g.dtype, device=g.device))
             if b:
-                b.append(torch.zeros((pad + H,), dtype=b[0].dtype, device=b[0].device))
-            self.width = self.g_off + H
+                b.append(torch.zeros((pad + H + tail,), dtype=b[0].dtype, device=b[0].device))
+            self.width = self.g_off + H + tail
         self.qkv = Linear(torch.cat(w, dim=0).contiguous(), torch.cat(b).contiguous() if b else None)
         self._q_only = None          # the query rows alone, made when a run first reads another run's cache
         del w, b
