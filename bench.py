@@ -13,9 +13,10 @@ read (every weight once plus the cache of the live requests) with the measured c
 `points` holds decode at batch 1 and 64; `check` compares the bfloat16 logits with the 32-bit path's at these
 layer sizes (two layers, untimed). Peaks come from MEASURED_PEAKS.json when it exists.
 
-`--design madevik` is another program under the same roof and leaves the default workload alone: prefill and decode of
-the Madevik design (gated linear attention, attention over a cached latent, routed experts) at layer sizes that resemble
-a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
+`--design madevik` and `--design movivik` are another program under the same roof and leave the default workload alone:
+prefill and decode of the Madevik design (gated linear attention, attention over a cached latent, routed experts) or of
+the Movivik design (chunked and parallel attention layers, linear attention with fixed decays, norms in front of and behind
+every part) at layer sizes that resemble a real model's, beside the Qwen3 dense shape of the same width, heads, layers and feed-forward weights (`--design-sizes`
 picks among them); one JSON line with both models' figures per size.
 
 The engine runs on one GPU; for --gpus above 1 the program says so and exits with 2.
@@ -124,19 +125,39 @@ def madevik_shape(width, heads, rank, experts, top, ff, runs, vocab=32768):
             "layers": [latent if i % 4 == 1 else gla for i in range(runs)]}
 
 
-# name -> (Madevik configuration, the Qwen3 dense shape of the same width, heads, layers and feed-forward weights)
+def movivik_shape(width, heads, kv_heads, ff, runs, chunk=1024, vocab=32768):
+    """Layers in pairs: two of chunked attention (YaRN-scaled interleaved rotation, biases), then two parallel layers (a
+    causal attention that rotates half of every head and norms q and k, beside linear attention with a fixed decay per
+    head); head size 128 throughout, a dense GELU-gated feed-forward in every layer."""
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": chunk},
+        "rot": {"base": 10000.0, "dims": 128, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    decay = [1.0 - 2.0 ** (-2 - 6 * h / max(1, heads - 1)) for h in range(heads)]
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "rot": {"base": 10000.0, "dims": 64}},
+        "right": {"heads": heads, "dim": 128, "vdim": 128, "decay": decay}}}
+    return {"architecture": "Movivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+            "layers": [att if i % 4 < 2 else par for i in range(runs)]}
+
+
+def _qwen3_shape(width, layers, heads, kv_heads, ffn):
+    return dict(QWEN3_8B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
+                intermediate_size=ffn, vocab_size=32768)
+
+
+# design -> name -> (the design's configuration, the Qwen3 dense shape of the same width, heads, layers and feed-forward weights)
 DESIGN_SIZES = {
-    "w2048": (madevik_shape(2048, 16, 128, 8, 2, 1024, 8),
-              dict(QWEN3_8B, hidden_size=2048, num_hidden_layers=8, num_attention_heads=16, num_key_value_heads=8,
-                   intermediate_size=8192, vocab_size=32768)),
-    "w4096": (madevik_shape(4096, 32, 256, 16, 4, 768, 4),
-              dict(QWEN3_8B, hidden_size=4096, num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=8,
-                   intermediate_size=12288, vocab_size=32768)),
+    "madevik": {"w2048": (madevik_shape(2048, 16, 128, 8, 2, 1024, 8), _qwen3_shape(2048, 8, 16, 8, 8192)),
+                "w4096": (madevik_shape(4096, 32, 256, 16, 4, 768, 4), _qwen3_shape(4096, 4, 32, 8, 12288))},
+    "movivik": {"w2048": (movivik_shape(2048, 16, 8, 8192, 8), _qwen3_shape(2048, 8, 16, 8, 8192)),
+                "w4096": (movivik_shape(4096, 32, 8, 12288, 4), _qwen3_shape(4096, 4, 32, 8, 12288))},
 }
 
 
 def design_bench(args) -> int:
-    """Prefill of one prompt and decode steps of a batch, device-timed, for the Madevik design and the Qwen3 dense shape
+    """Prefill of one prompt and decode steps of a batch, device-timed, for the chosen design and the Qwen3 dense shape
     beside it. Decode: `--batch` requests whose contexts (synthetic cache content, zero states) stand at `--context`."""
     import torch
 
@@ -145,15 +166,16 @@ def design_bench(args) -> int:
 
     ctx, batch, tokens = min(args.context, 2048), args.batch, min(PREFILL_TOKENS, args.context)
     steps, warmup = max(8, args.steps // 2), max(3, args.warmup)
-    out = {"design": "madevik", "dtype": "bf16", "data": "synthetic token ids, random-init weights", "prefill_tokens": tokens,
+    sizes = DESIGN_SIZES[args.design]
+    out = {"design": args.design, "dtype": "bf16", "data": "synthetic token ids, random-init weights", "prefill_tokens": tokens,
            "decode_batch": batch, "decode_context": ctx, "steps": steps, "warmup": warmup, "sizes": {}}
     out_tok = torch.empty(max(64, batch), dtype=torch.int32, device="cuda:0")
     for name in args.design_sizes.split(","):
-        if name not in DESIGN_SIZES:
-            print(f"bench.py: unknown size {name!r} (known: {', '.join(sorted(DESIGN_SIZES))})")
+        if name not in sizes:
+            print(f"bench.py: unknown size {name!r} (known: {', '.join(sorted(sizes))})")
             return 2
         record = {}
-        for model, cfg in zip(("madevik", "qwen3"), DESIGN_SIZES[name]):
+        for model, cfg in zip((args.design, "qwen3"), sizes[name]):
             engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=ctx + 64, page_size=PAGE,
                             num_pages=((batch + 1) * (ctx + 64) + 2 * tokens) // PAGE, max_batch_tokens=tokens + 64,
                             chunk=tokens, max_running=batch + 2)
@@ -235,8 +257,8 @@ def _tensors_of(obj, seen=None):
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("--design", default="", choices=["", "madevik"],
-                    help="madevik: time the Madevik design beside the Qwen3 dense shape of equal size instead of the default workload")
+    ap.add_argument("--design", default="", choices=["", "madevik", "movivik"],
+                    help="madevik, movivik: time that design beside the Qwen3 dense shape of equal size instead of the default workload")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="which of the sizes of --design, with commas between them")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

@@ -162,6 +162,7 @@ class _Signatures:
     jllm_head_prepare = [P, I, I, I, I, I, P, P, I, I, I, F, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
     jllm_head_gate = [P, I, I, P, I, I, I, I, P]
     jllm_norm_sum = [P, P, P, P, P, I, I, I, F, F, I, P]
+    jllm_norm_chain = [P, P, P, P, P, F, P, P, P, I, I, I, I, F, P]
     jllm_latent_norm_store = [P, I, I, P, I, P, P, ctypes.c_longlong, I, I, F, P]
     jllm_gemm_heads = [P, I, I, P, P, I, P, I, F, I, I, I, I, P]
     jllm_route_experts = [P, I, I, P, P, I, P, I, I, I, I, F, I, P]
@@ -364,6 +365,19 @@ def gemm_plain(a, w, out, bias=None, accumulate=False) -> None:
     _call("jllm_gemm_plain", a.data_ptr(), _DT[a.dtype], a.stride(0), w.data_ptr(), w.stride(0), _p(bias),
           _DT[bias.dtype] if bias is not None else F32, out.data_ptr(), _DT[out.dtype], out.stride(0),
           int(accumulate), a.shape[0], w.shape[0], a.shape[1], _stream())
+
+
+def norm_chain(x, a, gain_post, eps, b=None, gain_a=None, gain_b=None, scale: float = 1.0, next_out=None, gain_next=None) -> None:
+    """The norms between one part and the next in one launch: v = a, or scale * (rmsnorm(a) * gain_a + rmsnorm(b) * gain_b)
+    with two results; x += rmsnorm(v) * gain_post; and, with `next_out` (compute type, [rows, dim]), next_out = rmsnorm(x) *
+    gain_next. x, a, b float32 [rows, dim], contiguous; every gain of one stored type."""
+    assert x.dtype == a.dtype == torch.float32 and x.is_contiguous() and a.is_contiguous() and x.shape == a.shape
+    assert b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.shape == a.shape)
+    gains = [g for g in (gain_post, gain_a, gain_b, gain_next) if g is not None]
+    assert all(g.dtype == gain_post.dtype for g in gains) and (next_out is None or next_out.is_contiguous())
+    _call("jllm_norm_chain", x.data_ptr(), a.data_ptr(), _p(gain_a), _p(b), _p(gain_b), float(scale), gain_post.data_ptr(),
+          _p(gain_next), _p(next_out), _DT[next_out.dtype] if next_out is not None else F32, _DT[gain_post.dtype], x.shape[0],
+          x.shape[1], float(eps), _stream())
 
 
 def attention_plain(q, q_stride, k_cache, v_cache, out, row_seg, row_pos, block_tables, rows, heads, kv_heads,

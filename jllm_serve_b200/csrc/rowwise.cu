@@ -684,3 +684,76 @@ JLLM_EXPORT int jllm_norm_sum(float* x, const float* a, const void* gain_a, cons
                 VecRef{gain_b, gain_dtype}, dim, eps, scale, accumulate);
     return jllm_check_launch("norm_sum");
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The norms between a part's result and the next part's input, in one pass over a row (float32, `dim` values):
+//   v = a                                            (one result), or
+//   v = scale * (rmsnorm(a) * gain_a + rmsnorm(b) * gain_b)     (two results side by side, each normed)
+//   x += rmsnorm(v) * gain_post                      (the norm behind the part, then the residual sum)
+//   next = rmsnorm(x) * gain_next                    (optional: the norm in front of the part that follows; `next` has
+//                                                     the compute type)
+// The same arithmetic, in the same order, as norm_sum (twice) and rmsnorm one after the other. A block per row; the row
+// lives in shared memory between the steps.
+// ---------------------------------------------------------------------------------------------------
+template <typename Tnext>
+__global__ void __launch_bounds__(256)
+norm_chain_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gain_a, const float* __restrict__ b, VecRef gain_b,
+                  float scale, VecRef gain_post, VecRef gain_next, Tnext* __restrict__ next, int dim, float eps) {
+    extern __shared__ float row_smem[];     // dim floats
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const size_t row = (size_t)blockIdx.x * dim;
+    const float* pa = a + row;
+    if (b) {
+        const float* pb = b + row;
+        float sa = 0.f, sb = 0.f;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            sa = fmaf(pa[i], pa[i], sa);
+            sb = fmaf(pb[i], pb[i], sb);
+        }
+        sa = block_sum(sa, scratch);
+        sb = block_sum(sb, scratch);
+        const float ra = rms_scale(sa, dim, eps), rb = rms_scale(sb, dim, eps);
+        for (int i = threadIdx.x; i < dim; i += blockDim.x)
+            row_smem[i] = __fmul_rn(__fadd_rn(__fmul_rn(__fmul_rn(pa[i], ra), gain_a[i]), __fmul_rn(__fmul_rn(pb[i], rb), gain_b[i])), scale);
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) row_smem[i] = pa[i];
+    }
+    // (every thread reads back only what it wrote: no barrier is needed between the steps beyond those of the sums)
+    float sv = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) sv = fmaf(row_smem[i], row_smem[i], sv);
+    sv = block_sum(sv, scratch);
+    const float rv = rms_scale(sv, dim, eps);
+    float* px = x + row;
+    float sx = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = __fadd_rn(px[i], __fmul_rn(__fmul_rn(row_smem[i], rv), gain_post[i]));
+        px[i] = v;
+        row_smem[i] = v;
+        sx = fmaf(v, v, sx);
+    }
+    if (next == nullptr) return;
+    sx = block_sum(sx, scratch);
+    const float rx = rms_scale(sx, dim, eps);
+    Tnext* pn = next + row;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) pn[i] = from_float<Tnext>(__fmul_rn(__fmul_rn(row_smem[i], rx), gain_next[i]));
+}
+
+JLLM_EXPORT int jllm_norm_chain(float* x, const float* a, const void* gain_a, const float* b, const void* gain_b, float scale,
+                                const void* gain_post, const void* gain_next, void* next, int next_dtype, int gain_dtype,
+                                int rows, int dim, float eps, cudaStream_t stream) {
+    JLLM_REQUIRE(rows >= 0 && dim > 0 && a && gain_post && (!b || (gain_a && gain_b)) && (!next || gain_next),
+                 "norm_chain: rows=%d dim=%d", rows, dim);
+    JLLM_REQUIRE(dim <= 48 * 256, "norm_chain: a row of %d values is above %d", dim, 48 * 256);
+    if (rows == 0) return JLLM_OK;
+    const size_t smem = (size_t)dim * sizeof(float);
+    const VecRef ga{gain_a, gain_dtype}, gb{gain_b, gain_dtype}, gp{gain_post, gain_dtype}, gn{gain_next, gain_dtype};
+    if (next_dtype == JLLM_F32)
+        jllm_launch(norm_chain_kernel<float>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT, x, a, ga, b, gb, scale, gp,
+                    gn, (float*)next, dim, eps);
+    else
+        jllm_launch(norm_chain_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT, x, a, ga, b, gb,
+                    scale, gp, gn, (__nv_bfloat16*)next, dim, eps);
+    return jllm_check_launch("norm_chain");
+}

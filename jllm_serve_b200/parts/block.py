@@ -104,7 +104,8 @@ class SandwichNormBlock(PreNormBlock):
 
     The norms behind are RMS norms with gains of their own (`names.mixer_post_norm`, `names.feed_forward_post_norm`). A
     part's result goes into a float32 buffer (the part is told to write instead of add: `overwrite`; one that cannot gets
-    the buffer zeroed), and one kernel norms it and adds it to the stream."""
+    the buffer zeroed), and one kernel norms it, adds it to the stream and, behind the mixer, also makes the feed-forward's
+    normed input (`ops.norm_chain`)."""
 
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, position_encodings):
         super().__init__(spec, dim, tensors, prefix, runtime, position_encodings)
@@ -144,15 +145,21 @@ class SandwichNormBlock(PreNormBlock):
         rows = x.shape[0]
         xb = self.rt.buffer("normed", self.dim)[:rows]
         self.mixer_norm.forward(x, xb)
-        y = self._result(self.mixer, rows)
-        self.mixer.forward(xb, y, batch, cache)
-        ops.norm_sum(x, y, self.mixer_post_gain, self.eps)
+        branches = getattr(self.mixer, "forward_branches", None)
+        if branches is not None:
+            # a mixer of mixers hands over its branches' results as they are: their norms and their sum ride in the same
+            # launch as the norm behind the mixer
+            a, gain_a, b, gain_b, scale = branches(xb, batch, cache)
+        else:
+            a, gain_a, b, gain_b, scale = self._result(self.mixer, rows), None, None, None, 1.0
+            self.mixer.forward(xb, a, batch, cache)
         if self.feed_forward is None:
-            return
-        self.ffn_norm.forward(x, xb)
+            return ops.norm_chain(x, a, self.mixer_post_gain, self.eps, b, gain_a, gain_b, scale)
+        # ... and so does the norm in front of the feed-forward
+        ops.norm_chain(x, a, self.mixer_post_gain, self.eps, b, gain_a, gain_b, scale, next_out=xb, gain_next=self.ffn_norm.gain)
         y = self._result(self.feed_forward, rows)
         self.feed_forward.forward(xb, y, batch)
-        ops.norm_sum(x, y, self.ffn_post_gain, self.eps)
+        ops.norm_chain(x, y, self.ffn_post_gain, self.eps)
 
 
 register_block("sandwich_norm", SandwichNormBlock, replace=True)

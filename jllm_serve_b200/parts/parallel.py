@@ -37,6 +37,8 @@ class ParallelMixers(Mixer):
             self.branches.append(part)
             self.state_counts.append(sum(isinstance(n, FixedState) for n in needs_of(cls.cache_need(b))))
         self.gains = [tensors.pop(prefix + n) for n in spec.out_norms]
+        if len(self.branches) != 2:
+            self.forward_branches = None      # (one branch: the block norms the mixer's own result)
 
     @classmethod
     def wants(cls, spec, dim: int, prefix: str) -> dict:
@@ -57,7 +59,7 @@ class ParallelMixers(Mixer):
     def decode_bucket_cap(self, rows: int) -> int:
         return max(b.decode_bucket_cap(rows) for b in self.branches)
 
-    def forward(self, xb, x, batch, cache) -> None:
+    def _run_branches(self, xb, batch, cache) -> list:
         rows, outs, at = xb.shape[0], [], 0
         for i, (part, n) in enumerate(zip(self.branches, self.state_counts)):
             states = tuple(cache.states[at:at + n])
@@ -66,6 +68,17 @@ class ParallelMixers(Mixer):
             y = self.rt.buffer(f"parallel_branch{i}", self.dim, torch.float32)[:rows]
             part.forward(xb, y, batch, mine)
             outs.append(y)
+        return outs
+
+    def forward_branches(self, xb, batch, cache):
+        """The branches' results as they are, for a block that norms and adds them up in a launch of its own:
+        (a, gain_a, b, gain_b, weight), the result being weight * (rmsnorm(a) * gain_a + rmsnorm(b) * gain_b). None where
+        there is one branch only (the block then takes `forward`)."""
+        outs = self._run_branches(xb, batch, cache)
+        return outs[0], self.gains[0], outs[1], self.gains[1], self.spec.weight
+
+    def forward(self, xb, x, batch, cache) -> None:
+        outs = self._run_branches(xb, batch, cache)
         s = self.spec
         b, gb = (outs[1], self.gains[1]) if len(outs) > 1 else (None, None)
         ops.norm_sum(x, outs[0], self.gains[0], s.norm_eps, b, gb, scale=s.weight, accumulate=not self.overwrite)

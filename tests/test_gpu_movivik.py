@@ -352,7 +352,7 @@ class Checker:
         for rid, toks in self.sequences.items():
             missing = [p for p in range(len(toks)) if (rid, p) not in self.seen]
             assert not missing, f"{self.what}: no logits for {rid} positions {missing[:5]}"
-        tol = TOL[self.dtype] * self.scale * (1 if self.dtype == "float32" else 2)
+        tol = 2 * TOL[self.dtype] * self.scale        # (float32: a hundred-thousandth of the largest logit)
         worst = max(self.errors)
         over = [e for e in self.errors if e[0] > tol]
         rms = (self.err2 / max(self.ref2, 1e-300)) ** 0.5
