@@ -36,6 +36,15 @@ __global__ void gla_decay_kernel(float* __restrict__ z, float inv_tau, size_t to
 // kernels: this pass fills the decay table with decay[h] for every key channel of head h (its logarithm for the chunked
 // form; a decay of 0 becomes a logarithm of -1e30, whose differences are 0 or below -1e30 and never NaN), and applies
 // the activation of such a mixer to its projections in place: q, k, v <- silu (activation 1). A block per row.
+__device__ __forceinline__ float2 load_two(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load_two(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store_two(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_two(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 fixed_decay_prepare_kernel(T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, float* __restrict__ z,
@@ -44,21 +53,34 @@ fixed_decay_prepare_kernel(T* __restrict__ proj, int ld, int q_off, int k_off, i
     pdl_trigger();
     const size_t r = blockIdx.x;
     float* zr = z + r * heads * dk;
-    for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
-        const float d = decay[i / dk];
-        zr[i] = as_log ? fmaxf(logf(d), -1e30f) : d;
+    if ((dk & 3) == 0) {        // (the table's rows are whole float4s then: heads * dk is a multiple of 4, z is an allocation's start)
+        for (int i = threadIdx.x; i < heads * dk / 4; i += blockDim.x) {
+            const float d = decay[(4 * i) / dk], e = as_log ? fmaxf(logf(d), -1e30f) : d;
+            reinterpret_cast<float4*>(zr)[i] = make_float4(e, e, e, e);
+        }
+    } else {
+        for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
+            const float d = decay[i / dk];
+            zr[i] = as_log ? fmaxf(logf(d), -1e30f) : d;
+        }
     }
     if (!activation) return;
     T* row = proj + r * ld;
-    for (int i = threadIdx.x; i < heads * dk; i += blockDim.x) {
-        const float q = to_float(row[q_off + i]), k = to_float(row[k_off + i]);
-        row[q_off + i] = from_float<T>(q / (1.f + expf(-q)));
-        row[k_off + i] = from_float<T>(k / (1.f + expf(-k)));
-    }
-    for (int i = threadIdx.x; i < heads * dv; i += blockDim.x) {
-        const float v = to_float(row[v_off + i]);
-        row[v_off + i] = from_float<T>(v / (1.f + expf(-v)));
-    }
+    auto silu = [](float x) { return x / (1.f + expf(-x)); };
+    auto run = [&](int off, int n) {
+        T* p = row + off;
+        if ((n & 1) == 0 && (((uintptr_t)p) & (2 * sizeof(T) - 1)) == 0) {
+            for (int i = threadIdx.x; i < n / 2; i += blockDim.x) {
+                const float2 v = load_two(p + 2 * i);
+                store_two(p + 2 * i, silu(v.x), silu(v.y));
+            }
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] = from_float<T>(silu(to_float(p[i])));
+        }
+    };
+    run(q_off, heads * dk);
+    run(k_off, heads * dk);
+    run(v_off, heads * dv);
 }
 
 template <typename T>
@@ -541,6 +563,30 @@ gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, 
     }
 }
 
+// The same with a block per (row, head), for norms over many values (all heads of a row together: thousands): a warp
+// alone would walk them one after the other.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate, VecRef gain, T* __restrict__ y,
+                      int heads, int dv, float eps, float scale, int gate_kind) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x / heads, h = blockIdx.x - r * heads;
+    const float* src = o + ((size_t)r * heads + h) * dv;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+    const T* gp = gate + (size_t)r * ld_gate + (size_t)h * dv;
+    T* dst = y + ((size_t)r * heads + h) * dv;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+        const float gv = to_float(gp[i]);
+        const float gated = (gate_kind == 1 ? 1.f : gv) / (1.f + expf(-gv));
+        dst[i] = from_float<T>(__fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(src[i], inv), gain[i]), gated), scale));
+    }
+}
+
 }  // namespace
 
 JLLM_BOUNDS_READER(linear_attention)
@@ -655,6 +701,15 @@ JLLM_EXPORT int jllm_gated_head_norm(const float* o, const void* gate, int dtype
     if (rows == 0) return JLLM_OK;
     const VecRef g{gain, gain_dtype};
     const long long warps = (long long)rows * heads;
+    if (dv > 512 && warps <= 2147483647ll) {       // long norms: a block each
+        if (dtype == JLLM_F32)
+            jllm_launch(gated_row_norm_kernel<float>, dim3((unsigned)warps), dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
+                        (const float*)gate, ld_gate, g, (float*)y, heads, dv, eps, scale, gate_kind);
+        else
+            jllm_launch(gated_row_norm_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(256), 0, stream, LAUNCH_DEPENDENT, o,
+                        (const __nv_bfloat16*)gate, ld_gate, g, (__nv_bfloat16*)y, heads, dv, eps, scale, gate_kind);
+        return jllm_check_launch("gated_head_norm");
+    }
     const dim3 grid((unsigned)((warps + 7) / 8));
     if (dtype == JLLM_F32)
         jllm_launch(gated_head_norm_kernel<float>, grid, dim3(256), 0, stream, LAUNCH_DEPENDENT, o, (const float*)gate,

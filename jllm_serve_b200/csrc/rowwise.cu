@@ -506,6 +506,15 @@ JLLM_EXPORT int jllm_qk_norm_rope_store(void* qkv, int dtype, const void* q_gain
 // first key_dim values of a row, values the first value_dim). qkv [rows, row_stride]: queries at column q_off (heads x
 // key_dim), keys at k_off (kv_heads x key_dim), values at v_off (kv_heads x value_dim).
 // ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float2 load_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load_pair(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_prepare_kernel(T* __restrict__ qkv, int row_stride, int q_off, int k_off, int v_off, VecRef q_gain, VecRef k_gain,
@@ -526,7 +535,17 @@ head_prepare_kernel(T* __restrict__ qkv, int row_stride, int q_off, int k_off, i
     T* src = qkv + (size_t)r * row_stride +
              (is_q ? q_off + (size_t)h * key_dim
                    : is_k ? k_off + (size_t)(h - heads) * key_dim : v_off + (size_t)(h - heads - kv_heads) * value_dim);
-    for (int i = lane; i < n; i += 32) vec[i] = to_float(src[i]);
+    // (two values a lane and access where the row allows it: half as many loads and stores)
+    const bool pairs = (n & 1) == 0 && (((uintptr_t)src) & (2 * sizeof(T) - 1)) == 0;
+    if (pairs) {
+        for (int i = lane; i < n / 2; i += 32) {
+            const float2 v = load_pair(src + 2 * i);
+            vec[2 * i] = v.x;
+            vec[2 * i + 1] = v.y;
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) vec[i] = to_float(src[i]);
+    }
     __syncwarp();
     if (is_q || is_k) {
         if (pre_norm) {
@@ -565,7 +584,11 @@ head_prepare_kernel(T* __restrict__ qkv, int row_stride, int q_off, int k_off, i
         const size_t page = slot / page_size, off = slot % page_size;
         dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * cache_dim;
     }
-    for (int i = lane; i < n; i += 32) dst[i] = from_float<T>(vec[i]);
+    if (pairs && (((uintptr_t)dst) & (2 * sizeof(T) - 1)) == 0) {
+        for (int i = lane; i < n / 2; i += 32) store_pair(dst + 2 * i, vec[2 * i], vec[2 * i + 1]);
+    } else {
+        for (int i = lane; i < n; i += 32) dst[i] = from_float<T>(vec[i]);
+    }
 }
 
 JLLM_EXPORT int jllm_head_prepare(void* qkv, int dtype, int row_stride, int q_off, int k_off, int v_off, const void* q_gain,
@@ -625,10 +648,40 @@ __global__ void head_gate_kernel(T* __restrict__ att, int ld_att, const T* __res
     }
 }
 
+// The same for bfloat16 rows whose heads are whole 16-byte pieces: a thread takes 8 values of one head.
+__global__ void __launch_bounds__(256)
+head_gate_vec_kernel(__nv_bfloat16* __restrict__ att, int ld_att, const __nv_bfloat16* __restrict__ gate, int ld_gate,
+                     int value_dim, int pieces_per_row, unsigned total) {
+    pdl_wait();
+    pdl_trigger();
+    const unsigned i = blockIdx.x * 256u + threadIdx.x;
+    if (i >= total) return;
+    const unsigned r = i / pieces_per_row, c = (i - r * pieces_per_row) * 8;
+    const float g = __bfloat162float(gate[(size_t)r * ld_gate + c / value_dim]);
+    const float f = 1.f / (1.f + expf(-g));
+    uint4* p = reinterpret_cast<uint4*>(att + (size_t)r * ld_att + c);
+    uint4 v = *p;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(h[j]);
+        h[j] = __floats2bfloat162_rn(__fmul_rn(x.x, f), __fmul_rn(x.y, f));
+    }
+    *p = v;
+}
+
 JLLM_EXPORT int jllm_head_gate(void* att, int dtype, int ld_att, const void* gate, int ld_gate, int rows, int heads,
                                int value_dim, cudaStream_t stream) {
     JLLM_REQUIRE(rows >= 0 && heads > 0 && value_dim > 0, "head_gate: rows=%d heads=%d value_dim=%d", rows, heads, value_dim);
     if (rows == 0) return JLLM_OK;
+    if (dtype == JLLM_BF16 && value_dim % 8 == 0 && ld_att % 8 == 0 && ((uintptr_t)att % 16) == 0 &&
+        (long long)rows * heads * value_dim / 8 < 4000000000ll) {
+        const int pieces = heads * value_dim / 8;
+        const unsigned total_pieces = (unsigned)rows * pieces;
+        jllm_launch(head_gate_vec_kernel, dim3((total_pieces + 255) / 256), dim3(256), 0, stream, LAUNCH_DEPENDENT,
+                    (__nv_bfloat16*)att, ld_att, (const __nv_bfloat16*)gate, ld_gate, value_dim, pieces, total_pieces);
+        return jllm_check_launch("head_gate");
+    }
     const size_t total = (size_t)rows * heads * value_dim;
     const size_t most = (size_t)(jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1) * 16;
     const int blocks = (int)((total + 255) / 256 > most ? most : (total + 255) / 256);
@@ -740,6 +793,92 @@ norm_chain_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gai
     for (int i = threadIdx.x; i < dim; i += blockDim.x) pn[i] = from_float<Tnext>(__fmul_rn(__fmul_rn(row_smem[i], rx), gain_next[i]));
 }
 
+// The same with the row in registers (widths that are a multiple of 4, at most 1,024 * V values): a, b and x are all
+// requested before anything is computed, so the row pays one trip to memory instead of one per step. Value by value the
+// arithmetic is that of the kernel above (the partial sums of squares are grouped by thread as there).
+template <typename Tnext, int V>
+__global__ void __launch_bounds__(256)
+norm_chain_vec_kernel(float* __restrict__ x, const float* __restrict__ a, VecRef gain_a, const float* __restrict__ b,
+                      VecRef gain_b, float scale, VecRef gain_post, VecRef gain_next, Tnext* __restrict__ next, int dim, float eps) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const size_t row = (size_t)blockIdx.x * dim;
+    const int n4 = dim >> 2;
+    const float4* pa = reinterpret_cast<const float4*>(a + row);
+    const float4* pb = b ? reinterpret_cast<const float4*>(b + row) : nullptr;
+    float4* px = reinterpret_cast<float4*>(x + row);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 va[V], vb[V], vx[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        va[j] = i < n4 ? pa[i] : zero;
+        vb[j] = (pb && i < n4) ? pb[i] : zero;
+        vx[j] = i < n4 ? px[i] : zero;
+    }
+    auto squares = [](const float4& v, float acc) {
+        acc = fmaf(v.x, v.x, acc); acc = fmaf(v.y, v.y, acc); acc = fmaf(v.z, v.z, acc); return fmaf(v.w, v.w, acc);
+    };
+    if (pb) {
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) { sa = squares(va[j], sa); sb = squares(vb[j], sb); }
+        sa = block_sum(sa, scratch);
+        sb = block_sum(sb, scratch);
+        const float ra = rms_scale(sa, dim, eps), rb = rms_scale(sb, dim, eps);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int i = 4 * (threadIdx.x + 256 * j);
+            if (i >= dim) break;
+            float* pva = reinterpret_cast<float*>(&va[j]);
+            const float* pvb = reinterpret_cast<const float*>(&vb[j]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                pva[c] = __fmul_rn(__fadd_rn(__fmul_rn(__fmul_rn(pva[c], ra), gain_a[i + c]), __fmul_rn(__fmul_rn(pvb[c], rb), gain_b[i + c])), scale);
+        }
+    }
+    float sv = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; ++j) sv = squares(va[j], sv);
+    sv = block_sum(sv, scratch);
+    const float rv = rms_scale(sv, dim, eps);
+    float sx = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int i4 = threadIdx.x + 256 * j;
+        if (i4 >= n4) break;
+        const float* pva = reinterpret_cast<const float*>(&va[j]);
+        float* pvx = reinterpret_cast<float*>(&vx[j]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) pvx[c] = __fadd_rn(pvx[c], __fmul_rn(__fmul_rn(pva[c], rv), gain_post[4 * i4 + c]));
+        px[i4] = vx[j];
+        sx = squares(vx[j], sx);
+    }
+    if (next == nullptr) return;
+    sx = block_sum(sx, scratch);
+    const float rx = rms_scale(sx, dim, eps);
+    Tnext* pn = next + row;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int i4 = threadIdx.x + 256 * j;
+        if (i4 >= n4) break;
+        const float* pvx = reinterpret_cast<const float*>(&vx[j]);
+        float o[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[c] = __fmul_rn(__fmul_rn(pvx[c], rx), gain_next[4 * i4 + c]);
+        if constexpr (sizeof(Tnext) == 4) {
+            reinterpret_cast<float4*>(pn)[i4] = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+            uint2 p;
+            p.x = *reinterpret_cast<uint32_t*>(&lo);
+            p.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(pn)[i4] = p;
+        }
+    }
+}
+
 JLLM_EXPORT int jllm_norm_chain(float* x, const float* a, const void* gain_a, const float* b, const void* gain_b, float scale,
                                 const void* gain_post, const void* gain_next, void* next, int next_dtype, int gain_dtype,
                                 int rows, int dim, float eps, cudaStream_t stream) {
@@ -749,6 +888,22 @@ JLLM_EXPORT int jllm_norm_chain(float* x, const float* a, const void* gain_a, co
     if (rows == 0) return JLLM_OK;
     const size_t smem = (size_t)dim * sizeof(float);
     const VecRef ga{gain_a, gain_dtype}, gb{gain_b, gain_dtype}, gp{gain_post, gain_dtype}, gn{gain_next, gain_dtype};
+    if (dim % 4 == 0 && dim <= 8192 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 &&
+        ((uintptr_t)next % 16) == 0) {
+#define JLLM_CHAIN(T, V)                                                                                                      \
+    jllm_launch(norm_chain_vec_kernel<T, V>, dim3(rows), dim3(256), 0, stream, LAUNCH_DEPENDENT, x, a, ga, b, gb, scale, gp, gn, \
+                (T*)next, dim, eps)
+        const int v = (dim / 4 + 255) / 256;
+        if (next_dtype == JLLM_F32) {
+            if (v <= 1) JLLM_CHAIN(float, 1); else if (v <= 2) JLLM_CHAIN(float, 2); else if (v <= 4) JLLM_CHAIN(float, 4);
+            else JLLM_CHAIN(float, 8);
+        } else {
+            if (v <= 1) JLLM_CHAIN(__nv_bfloat16, 1); else if (v <= 2) JLLM_CHAIN(__nv_bfloat16, 2);
+            else if (v <= 4) JLLM_CHAIN(__nv_bfloat16, 4); else JLLM_CHAIN(__nv_bfloat16, 8);
+        }
+#undef JLLM_CHAIN
+        return jllm_check_launch("norm_chain");
+    }
     if (next_dtype == JLLM_F32)
         jllm_launch(norm_chain_kernel<float>, dim3(rows), dim3(256), smem, stream, LAUNCH_DEPENDENT, x, a, ga, b, gb, scale, gp,
                     gn, (float*)next, dim, eps);

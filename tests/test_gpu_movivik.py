@@ -211,11 +211,12 @@ def test_decode_attention_stops_at_a_chunks_edge(splits, H, G, hd, page, chunk):
         rows_close(out, want, f"decode dealt out, chunk {chunk}")
 
 
+@pytest.mark.parametrize("heads, dv", [(5, 24), (3, 7), (16, 128), (6, 64)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_head_gate_norm_sum_and_gated_norm(dtype):
+def test_head_gate_norm_sum_and_gated_norm(dtype, heads, dv):
     o_ = ops()
     g = torch.Generator().manual_seed(4)
-    rows, heads, dv, dim = 13, 5, 24, 200
+    rows, dim = 13, 200
     att = torch.randn(rows, heads * dv + 8, generator=g).to(dtype)
     gate = torch.randn(rows, heads + 3, generator=g).to(dtype)
     dev = att.to(DEV)
@@ -239,6 +240,31 @@ def test_head_gate_norm_sum_and_gated_norm(dtype):
     y = torch.empty(rows, heads * dv, dtype=dtype, device=DEV)
     o_.gated_head_norm(o.to(DEV), gates.to(DEV)[:, 16:], gain.to(DEV), 1e-5, 1.0, y, 1, heads * dv, "sigmoid")
     close(y, P.norm(o.double(), gain.double(), 1e-5) * torch.sigmoid(gates[:, 16:].double()), dtype, "norm over all heads, gated")
+
+
+@pytest.mark.parametrize("dim", [56, 203, 2048, 5000, 8196])
+@pytest.mark.parametrize("two", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_norms_between_two_parts_in_one_launch(dim, two, dtype):
+    """x += norm(v), v one result or half the sum of two normed results; and the next part's normed input. Widths that the
+    register form takes and widths that it leaves to the general form."""
+    o_ = ops()
+    g = torch.Generator().manual_seed(dim)
+    rows, eps = 7, 1e-5
+    a, b, x = torch.randn(rows, dim, generator=g) * 40, torch.randn(rows, dim, generator=g) * 0.02, torch.randn(rows, dim, generator=g)
+    gains = [(1 + 0.2 * torch.randn(dim, generator=g)).to(dtype) for _ in range(4)]
+    ga, gb, gp, gn = [t.double() for t in gains]
+    v = 0.5 * (P.norm(a.double(), ga, eps) + P.norm(b.double(), gb, eps)) if two else a.double()
+    want_x = x.double() + P.norm(v, gp, eps)
+    xd, nxt = x.to(DEV), torch.full((rows, dim), float("nan"), dtype=dtype, device=DEV)
+    dg = [t.to(DEV) for t in gains]
+    o_.norm_chain(xd, a.to(DEV), dg[2], eps, b.to(DEV) if two else None, dg[0] if two else None, dg[1] if two else None, 0.5,
+                  next_out=nxt, gain_next=dg[3])
+    close(xd, want_x, torch.float32, "the stream")
+    close(nxt, P.norm(want_x, gn, eps), dtype, "the next part's input")
+    xd = x.to(DEV)
+    o_.norm_chain(xd, a.to(DEV), dg[2], eps, b.to(DEV) if two else None, dg[0] if two else None, dg[1] if two else None, 0.5)
+    close(xd, want_x, torch.float32, "the stream alone")
 
 
 @pytest.mark.parametrize("rows", [1, 9, 40, 100, 300, 2100])
