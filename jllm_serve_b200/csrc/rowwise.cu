@@ -591,6 +591,115 @@ head_prepare_kernel(T* __restrict__ qkv, int row_stride, int q_off, int k_off, i
     }
 }
 
+// The same for bfloat16 heads of 64, 128 or 256 values of one width (key_dim = value_dim = cache_dim = 8 * LANES): a head
+// in the registers of LANES lanes, 8 neighbouring values and one 16-byte access each, 32 / LANES heads a warp. An
+// interleaved pair lies inside a lane; the partner of a half pair lies rotary_dim / 16 lanes away (rotary_dim a multiple
+// of 16) and comes by shuffles. Value by value the arithmetic is that of the kernel above; the sums of squares are grouped
+// by lane.
+template <int LANES>
+__global__ void __launch_bounds__(256)
+head_prepare_vec_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride, int q_off, int k_off, int v_off, VecRef q_gain,
+                        VecRef k_gain, int pre_norm, int post_norm, float eps, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, int rotary_dim, int pairing, const int* __restrict__ positions,
+                        const int* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                        int heads, int kv_heads, int page_size, int num_slots, int heads_total, long long items) {
+    constexpr int HD = 8 * LANES, PER_WARP = 32 / LANES;
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, sub = lane % LANES;
+    const long long item = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * PER_WARP + lane / LANES;
+    const bool live = item < items;
+    const int r = live ? (int)(item / heads_total) : 0, h = live ? (int)(item % heads_total) : 0;
+    const bool is_q = h < heads, is_k = !is_q && h < heads + kv_heads;
+    __nv_bfloat16* src = qkv + (size_t)r * row_stride +
+                         (is_q ? q_off + (size_t)h * HD : is_k ? k_off + (size_t)(h - heads) * HD
+                                                               : v_off + (size_t)(h - heads - kv_heads) * HD);
+    float x[8];
+    {
+        const uint4 u = live ? *reinterpret_cast<const uint4*>(src + sub * 8) : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p[i]);
+            x[2 * i] = f.x;
+            x[2 * i + 1] = f.y;
+        }
+    }
+    auto group_sum = [&](float v) {
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+    };
+    const bool turns = is_q || is_k;      // (values are only copied; all lanes still take part in the shuffles)
+    if (pre_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+        const float s = rms_scale(group_sum(ss), HD, eps);
+        const VecRef g = is_q ? q_gain : k_gain;
+        if (turns) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(__fmul_rn(x[i], s), g[sub * 8 + i]);
+        }
+    }
+    if (rotary_dim > 0) {
+        const int half = rotary_dim >> 1, e0 = sub * 8;
+        const float* c = cos_t + (size_t)positions[r] * half;
+        const float* sn = sin_t + (size_t)positions[r] * half;
+        if (pairing) {       // pairs (2i, 2i + 1): inside the lane
+            if (turns && e0 < rotary_dim) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int pr = e0 / 2 + i;
+                    const float a = x[2 * i], b = x[2 * i + 1];
+                    x[2 * i] = __fsub_rn(__fmul_rn(a, c[pr]), __fmul_rn(b, sn[pr]));
+                    x[2 * i + 1] = __fadd_rn(__fmul_rn(b, c[pr]), __fmul_rn(a, sn[pr]));
+                }
+            }
+        } else {             // pairs (i, i + half): the partner's 8 values lie half / 8 lanes up or down
+            const int shift = half >> 3;
+            const bool low = e0 < half, in = e0 < rotary_dim;
+            const int from = (lane / LANES) * LANES + (low ? sub + shift : sub - shift);
+            float y[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[i] = __shfl_sync(0xffffffffu, x[i], (in ? from : lane) & 31);
+            if (turns && in) {
+                const int p0 = low ? e0 : e0 - half;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    // low: (a, b) = (mine, partner) -> a cos - b sin; high: (a, b) = (partner, mine) -> b cos + a sin
+                    x[i] = low ? __fsub_rn(__fmul_rn(x[i], c[p0 + i]), __fmul_rn(y[i], sn[p0 + i]))
+                               : __fadd_rn(__fmul_rn(x[i], c[p0 + i]), __fmul_rn(y[i], sn[p0 + i]));
+                }
+            }
+        }
+    }
+    if (post_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+        const float s = rms_scale(group_sum(ss), HD, eps);
+        if (turns) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], s);
+        }
+    }
+    if (!live) return;
+    __nv_bfloat16* dst = src;
+    if (!is_q) {
+        const int kvh = is_k ? h - heads : h - heads - kv_heads;
+        const int slot = slots[r];
+        if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;      // checked build: the write is dropped
+        const size_t page = slot / page_size, off = slot % page_size;
+        dst = (is_k ? k_cache : v_cache) + ((page * kv_heads + kvh) * page_size + off) * HD;
+    }
+    uint4 o;
+    __nv_bfloat162* q2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst + sub * 8) = o;
+}
+
 JLLM_EXPORT int jllm_head_prepare(void* qkv, int dtype, int row_stride, int q_off, int k_off, int v_off, const void* q_gain,
                                   const void* k_gain, int gain_dtype, int pre_norm, int post_norm, float eps,
                                   const float* cos_t, const float* sin_t, int rotary_dim, int pairing, const int* positions,
@@ -614,6 +723,21 @@ JLLM_EXPORT int jllm_head_prepare(void* qkv, int dtype, int row_stride, int q_of
     const dim3 grid((unsigned)((items + 7) / 8));
     const size_t smem = (size_t)8 * width * sizeof(float);
     const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    if (dtype == JLLM_BF16 && key_dim == value_dim && (!write_kv || cache_dim == key_dim) &&
+        (key_dim == 64 || key_dim == 128 || key_dim == 256) && (pairing ? rotary_dim % 8 == 0 : rotary_dim % 16 == 0) &&
+        row_stride % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 && ((uintptr_t)qkv % 16) == 0 &&
+        ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0) {
+        const int lanes = key_dim / 8;
+        const long long per_block = 8 * (32 / lanes);
+        const dim3 vgrid((unsigned)((items + per_block - 1) / per_block));
+#define JLLM_HEAD_VEC(L)                                                                                                      \
+    jllm_launch(head_prepare_vec_kernel<L>, vgrid, dim3(256), 0, stream, LAUNCH_DEPENDENT, (__nv_bfloat16*)qkv, row_stride, q_off, \
+                k_off, v_off, qg, kg, pre_norm, post_norm, eps, cos_t, sin_t, rotary_dim, pairing, positions, slots,              \
+                (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads, page_size, num_slots, heads_total, items)
+        if (lanes == 8) JLLM_HEAD_VEC(8); else if (lanes == 16) JLLM_HEAD_VEC(16); else JLLM_HEAD_VEC(32);
+#undef JLLM_HEAD_VEC
+        return jllm_check_launch("head_prepare");
+    }
     if (dtype == JLLM_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(head_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         jllm_launch(head_prepare_kernel<float>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (float*)qkv, row_stride, q_off,

@@ -71,7 +71,14 @@ _E_PAR = (_att(2, 2, 32, 16, 0.2, _rot(16, 700.0)), _lin(3, 20, 12, (0.9, 0.6, 0
 MOVIVIK_E = {"architecture": "Movivik", "width": 48, "vocab": 88, "norm": {"eps": 3e-6}, "layers": [
     _parallel(*_E_PAR, 20), _parallel(*_E_PAR, 20, weights_of=0), _parallel(*_E_PAR, 20, weights_of=1)]}
 
-MOVIVIK = {"A": MOVIVIK_A, "B": MOVIVIK_B, "C": MOVIVIK_C, "D": MOVIVIK_D, "E": MOVIVIK_E}
+# F: nothing is a multiple of 4 or 8 (the products fall to the CUDA-core kernel in both precisions, no access is a
+# vector's): width 50, heads of 10, 6 and 14 values, a rotation of 6 of them, a chunk of 7 positions, a prime vocabulary;
+# the parallel layer comes first and the attention layer borrows nothing
+MOVIVIK_F = {"architecture": "Movivik", "width": 50, "vocab": 61, "norm": {"eps": 1e-4}, "layers": [
+    _parallel(_att(3, 1, 10, 6, 0.4, _rot(6, 20.0)), _lin(3, 5, 7, (0.3, 0.8, 0.99)), 21),
+    _attention(_att(2, 2, 14, 9, 0.3, _rot(6, 70.0, (1.5, 12, 3.0, 1.0)), chunk=7), 13)]}
+
+MOVIVIK = {"A": MOVIVIK_A, "B": MOVIVIK_B, "C": MOVIVIK_C, "D": MOVIVIK_D, "E": MOVIVIK_E, "F": MOVIVIK_F}
 
 
 def sharpen(tensors: dict, config: dict) -> dict:

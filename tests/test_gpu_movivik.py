@@ -42,9 +42,12 @@ def i32(v):
 @pytest.mark.parametrize("heads, kv_heads, dk, dv, dims, pairing, unit, pre", [
     (4, 2, 24, 16, 16, "interleaved", False, False), (3, 3, 16, 24, 8, "half", True, False),
     (8, 1, 128, 128, 32, "half", True, False), (6, 1, 96, 64, 96, "interleaved", False, False),
-    (2, 2, 64, 64, 64, "half", False, True), (1, 1, 40, 300, 0, "half", True, True), (5, 1, 272, 8, 2, "interleaved", True, False)])
+    (2, 2, 64, 64, 64, "half", False, True), (1, 1, 40, 300, 0, "half", True, True), (5, 1, 272, 8, 2, "interleaved", True, False),
+    (3, 1, 256, 256, 64, "half", True, True), (5, 5, 64, 64, 16, "interleaved", True, False), (4, 2, 128, 128, 128, "interleaved", False, True),
+    (2, 1, 256, 256, 256, "half", False, False), (7, 1, 64, 64, 48, "half", True, False), (2, 2, 128, 128, 0, "half", True, True)])
+@pytest.mark.parametrize("aligned", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_head_preparation(heads, kv_heads, dk, dv, dims, pairing, unit, pre, dtype):
+def test_head_preparation(heads, kv_heads, dk, dv, dims, pairing, unit, pre, dtype, aligned):
     """Rotation of either pairing over part of a head, the unit norm behind it, a norm with gains in front, keys and values
     of different widths into cache rows as wide as the wider; positions far apart."""
     g = torch.Generator().manual_seed(heads * 100 + dk)
@@ -54,8 +57,12 @@ def test_head_preparation(heads, kv_heads, dk, dv, dims, pairing, unit, pre, dty
     f, amp = P.rotary_frequencies(rot)
     angle = torch.arange(1024, dtype=torch.float64)[:, None] * torch.tensor(f, dtype=torch.float64)[None, :]
     cos, sin = (torch.cos(angle) * amp).float().to(DEV), (torch.sin(angle) * amp).float().to(DEV)
-    q_off, k_off, v_off = 8, 8 + heads * dk + 3, 8 + heads * dk + 3 + kv_heads * dk + 5
-    width = v_off + kv_heads * dv + 2
+    # `aligned`: every piece starts at a multiple of 8 values (what the register form of the kernel wants; heads of 64, 128
+    # and 256 values then take it), else anywhere
+    gap = (8, 16, 8) if aligned else (3, 5, 2)
+    q_off, k_off = 8, 8 + heads * dk + gap[0]
+    v_off = k_off + kv_heads * dk + gap[1]
+    width = -(-(v_off + kv_heads * dv + gap[2]) // 8) * 8 if aligned else v_off + kv_heads * dv + gap[2]
     qkv = (torch.randn(rows, width, generator=g) * 2).to(dtype)
     gq, gk = (1 + 0.3 * torch.randn(dk, generator=g)).bfloat16(), (1 + 0.3 * torch.randn(dk, generator=g)).bfloat16()
     cache_dim = max(dk, dv)
@@ -446,10 +453,11 @@ def test_every_cut_of_the_same_requests_gives_the_plain_logits(name, dtype, way)
 
 
 @pytest.mark.parametrize("way", ["prompt, then token by token", "mixed, slots and pages used again"])
-@pytest.mark.parametrize("name", ["D", "E"])
+@pytest.mark.parametrize("name", ["D", "E", "F"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_models_of_one_kind_of_layer_only(name, dtype, way):
-    """Pages and no state at all; states beside pages in every layer, with borrowed weights."""
+def test_models_of_one_kind_of_layer_only_and_of_odd_sizes(name, dtype, way):
+    """Pages and no state at all; states beside pages in every layer, with borrowed weights; sizes that are multiples of
+    nothing."""
     seqs = sequences_for(name, (3, 70, 1, 141, 18), seed=31)
     run_trace(name, dtype, WAYS[way](seqs), seqs, way)
 
