@@ -13,6 +13,8 @@
 // A segment is a run of consecutive rows of one request (a prompt portion, or one decoded token); its state lies in
 // `state[slot]` ([slots, heads, dk, dv]), is read at the segment's first token and written back after its last. The
 // same kernel serves a prompt and a decode step; the float32 and the bfloat16 path differ in the type of q, k, v only.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -53,7 +55,9 @@ fixed_decay_prepare_kernel(T* __restrict__ proj, int ld, int q_off, int k_off, i
     pdl_trigger();
     const size_t r = blockIdx.x;
     float* zr = z + r * heads * dk;
-    if ((dk & 3) == 0) {        // (the table's rows are whole float4s then: heads * dk is a multiple of 4, z is an allocation's start)
+    if (z == nullptr) {
+        // (the tensor-core form of the chunks takes the decays themselves: no table)
+    } else if ((dk & 3) == 0) {        // (the table's rows are whole float4s then: heads * dk is a multiple of 4, z is an allocation's start)
         for (int i = threadIdx.x; i < heads * dk / 4; i += blockDim.x) {
             const float d = decay[(4 * i) / dk], e = as_log ? fmaxf(logf(d), -1e30f) : d;
             reinterpret_cast<float4*>(zr)[i] = make_float4(e, e, e, e);
@@ -587,6 +591,279 @@ gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
     }
 }
 
+
+// ---- prompt portions of the fixed-decay form on the tensor cores (bfloat16 path) ---------------------------------------
+// With ONE decay d per head the decay's powers are scalars per token, so a chunk of 64 tokens is four matrix products
+// whose operands are the projections themselves (q, k, v: bfloat16 as the stacked product left them) and whose decay
+// weights are applied in float32:
+//     P[t, s] = (q_t . k_s) d^(t - s)  for s <= t, else 0                  scores from the tensor cores, float32; times the power
+//     o_t     = sum_s P[t, s] v_s  +  d^(t + 1) (q_t^T S0)                  S0: the state in front of the chunk
+//     S       = d^n S0 + sum_s (d^(n - 1 - s) k_s) v_s^T                    n: the chunk's tokens
+// Everything float32 that becomes a tensor-core operand (P, the weighted keys, the state) is split into a bfloat16 value
+// and the bfloat16 of what that rounding left over, and multiplied as two operands: 16 bits of mantissa instead of 8, the
+// accumulation in float32. The state itself stays in float32 registers from the first chunk to the last (it is the
+// accumulator of the last product) and is read from and written to its slot once per portion.
+//
+// A block owns 64 value columns of one (segment, head): the state's columns do not depend on one another. Eight warps:
+// warp w takes the 16 tokens (w & 3) of the chunk for P and o, with half (w >> 2) of the keys or of the block's value
+// columns, and for the state the 16 value columns (w & 3) with half (w >> 2) of the key channels. Operands lie in shared
+// memory with the contraction index contiguous (rows padded by 16 bytes: a warp's fragment loads hit 32 different
+// banks), so every product is the same "row times row" tile loop.
+namespace lightning {
+
+constexpr int C = 64;            // tokens of a chunk
+constexpr int DVB = 64;          // value columns of a block
+constexpr int LDC = C + 8;       // row length of operands whose contraction runs over the chunk's tokens
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// the A fragment (16 rows from `row0`, 16 contraction values from `k0`) of a row-major operand
+__device__ __forceinline__ void load_a(uint32_t (&a)[4], const __nv_bfloat16* m, int ld, int row0, int k0, int g, int t) {
+    const __nv_bfloat16* p = m + (size_t)(row0 + g) * ld + k0 + 2 * t;
+    a[0] = *reinterpret_cast<const uint32_t*>(p);
+    a[1] = *reinterpret_cast<const uint32_t*>(p + 8 * ld);
+    a[2] = *reinterpret_cast<const uint32_t*>(p + 8);
+    a[3] = *reinterpret_cast<const uint32_t*>(p + 8 * ld + 8);
+}
+
+// the B fragment (8 output columns from `n0`, 16 contraction values from `k0`) of an operand stored [columns][contraction]
+__device__ __forceinline__ void load_b(uint32_t& b0, uint32_t& b1, const __nv_bfloat16* m, int ld, int n0, int k0, int g, int t) {
+    const __nv_bfloat16* p = m + (size_t)(n0 + g) * ld + k0 + 2 * t;
+    b0 = *reinterpret_cast<const uint32_t*>(p);
+    b1 = *reinterpret_cast<const uint32_t*>(p + 8);
+}
+
+// v = hi + lo with hi = bfloat16(v), lo = bfloat16(v - hi)
+__device__ __forceinline__ void split(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+__device__ __forceinline__ void store_split2(__nv_bfloat16* hi, __nv_bfloat16* lo, float a, float b) {
+    __nv_bfloat16 ah, al, bh, bl;
+    split(a, ah, al);
+    split(b, bh, bl);
+    __nv_bfloat162 h2, l2;
+    h2.x = ah; h2.y = bh; l2.x = al; l2.y = bl;
+    *reinterpret_cast<__nv_bfloat162*>(hi) = h2;
+    *reinterpret_cast<__nv_bfloat162*>(lo) = l2;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(256)
+chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+             const float* __restrict__ head_decay, float* __restrict__ state, const int* __restrict__ seg_start,
+             const int* __restrict__ seg_len, const int* __restrict__ state_slots, float* __restrict__ o, int heads, int dv,
+             int num_slots, float q_scale) {
+    constexpr int LDQ = DK + 8;          // row length of operands whose contraction runs over the key channels
+    constexpr int NS = DK / 16;          // 8-wide tiles of a warp's half of the key channels
+    extern __shared__ __align__(16) unsigned char lightning_smem[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lightning_smem);   // [C][LDQ]     q
+    __nv_bfloat16* Ks = Qs + C * LDQ;                                       // [C][LDQ]     k
+    __nv_bfloat16* Vt = Ks + C * LDQ;                                       // [DVB][LDC]   v, transposed
+    __nv_bfloat16* Kh = Vt + DVB * LDC;                                     // [DK][LDC]    weighted k, transposed: value
+    __nv_bfloat16* Kl = Kh + DK * LDC;                                      //              ... and what its rounding left
+    __nv_bfloat16* Ph = Kl + DK * LDC;                                      // [C][LDC]     P
+    __nv_bfloat16* Pl = Ph + C * LDC;
+    __nv_bfloat16* Sh = Pl + C * LDC;                                       // [DVB][LDQ]   the state, transposed
+    __nv_bfloat16* Sl = Sh + DVB * LDQ;
+    float* pw = reinterpret_cast<float*>(Sl + DVB * LDQ);                   // [C + 1]      d^0 .. d^C
+    pdl_wait();
+    pdl_trigger();
+    const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DVB;
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int mt = w & 3, half = w >> 2;
+    const int first = seg_start[seg], n = seg_len[seg], slot = state_slots[seg];
+    if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;
+    float* S = state + (((size_t)slot * heads + h) * DK) * dv;
+    if (tid <= C) {
+        const float d = head_decay[h];
+        pw[tid] = expf((float)tid * fmaxf(logf(d), -1e30f));      // (a decay of 0: d^0 = 1, every other power 0)
+    }
+    // the state, transposed: this thread's values are (value column c0 + mt * 16 + g [+ 8], key channel half * DK / 2 + j * 8 + 2 t [+ 1])
+    float sacc[NS][4];
+    const int vrow = mt * 16 + g, kcol0 = half * (DK / 2) + 2 * t;
+#pragma unroll
+    for (int j = 0; j < NS; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = c0 + vrow + (e >> 1) * 8, ch = kcol0 + j * 8 + (e & 1);
+            sacc[j][e] = col < dv ? S[(size_t)ch * dv + col] : 0.f;
+        }
+    auto park_state = [&]() {
+#pragma unroll
+        for (int j = 0; j < NS; ++j) {
+            const int ch = kcol0 + j * 8;
+            store_split2(Sh + (size_t)vrow * LDQ + ch, Sl + (size_t)vrow * LDQ + ch, sacc[j][0], sacc[j][1]);
+            store_split2(Sh + (size_t)(vrow + 8) * LDQ + ch, Sl + (size_t)(vrow + 8) * LDQ + ch, sacc[j][2], sacc[j][3]);
+        }
+    };
+    park_state();
+    const size_t row_o = (size_t)heads * dv;
+    // a chunk's q, k (16-byte pieces; neighbouring lanes take neighbouring tokens, so that the transposed stores fall into
+    // different banks) and v in registers: requested a chunk ahead
+    constexpr int QI = C * (DK / 8) / 256, VI = C * (DVB / 8) / 256;
+    uint4 fq[QI], fk[QI], fv[VI];
+    auto fetch = [&](int t0) {
+        const int nt = min(C, n - t0);
+#pragma unroll
+        for (int u = 0; u < QI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            fq[u] = fk[u] = make_uint4(0, 0, 0, 0);
+            if (srow < nt) {
+                const __nv_bfloat16* base = proj + (size_t)(first + t0 + srow) * ld + (size_t)h * DK + piece * 8;
+                fq[u] = *reinterpret_cast<const uint4*>(base + q_off);
+                fk[u] = *reinterpret_cast<const uint4*>(base + k_off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < VI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            fv[u] = make_uint4(0, 0, 0, 0);
+            if (srow < nt && c0 + piece * 8 < dv)
+                fv[u] = *reinterpret_cast<const uint4*>(proj + (size_t)(first + t0 + srow) * ld + v_off + (size_t)h * dv + c0 + piece * 8);
+        }
+    };
+    if (n > 0) fetch(0);
+    for (int t0 = 0; t0 < n; t0 += C) {
+        const int nt = min(C, n - t0);
+        __syncthreads();       // pw and the parked state are written; the tiles of the chunk before are no longer read
+        // ---- the chunk's q, k, v, fetched while the chunk before was worked on, go into shared memory (the weighted k
+        //      and v transposed on their way); then the next chunk's are requested ----
+#pragma unroll
+        for (int u = 0; u < QI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            *reinterpret_cast<uint4*>(Qs + (size_t)srow * LDQ + piece * 8) = fq[u];
+            *reinterpret_cast<uint4*>(Ks + (size_t)srow * LDQ + piece * 8) = fk[u];
+            const float wgt = srow < nt ? pw[nt - 1 - srow] : 0.f;
+            const __nv_bfloat16* kv = reinterpret_cast<const __nv_bfloat16*>(&fk[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat16 hi, lo;
+                split(__bfloat162float(kv[i]) * wgt, hi, lo);
+                Kh[(size_t)(piece * 8 + i) * LDC + srow] = hi;
+                Kl[(size_t)(piece * 8 + i) * LDC + srow] = lo;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < VI; ++u) {
+            const int e = tid + u * 256, piece = e / C, srow = e - piece * C;
+            const __nv_bfloat16* vv = reinterpret_cast<const __nv_bfloat16*>(&fv[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) Vt[(size_t)(piece * 8 + i) * LDC + srow] = vv[i];
+        }
+        if (t0 + C < n) fetch(t0 + C);
+        __syncthreads();
+        // ---- P = q k^T for this warp's 16 tokens and 32 keys, times the decay's powers; parked as two operands ----
+        float acc[4][4] = {};
+        float o2[4][4] = {};
+        for (int k0 = 0; k0 < DK; k0 += 16) {
+            uint32_t a[4];
+            load_a(a, Qs, LDQ, mt * 16, k0, g, t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t b0, b1;
+                load_b(b0, b1, Ks, LDQ, half * 32 + j * 8, k0, g, t);
+                mma_bf16(acc[j], a, b0, b1);
+                // ... and q^T S0 for this warp's 16 tokens and 32 value columns (the state as two operands)
+                load_b(b0, b1, Sh, LDQ, half * 32 + j * 8, k0, g, t);
+                mma_bf16(o2[j], a, b0, b1);
+                load_b(b0, b1, Sl, LDQ, half * 32 + j * 8, k0, g, t);
+                mma_bf16(o2[j], a, b0, b1);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int key = half * 32 + j * 8 + 2 * t;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int tok = mt * 16 + g + hrow * 8;
+                const float p0 = key <= tok ? __fmul_rn(__fmul_rn(acc[j][2 * hrow], q_scale), pw[tok - key]) : 0.f;
+                const float p1 = key + 1 <= tok ? __fmul_rn(__fmul_rn(acc[j][2 * hrow + 1], q_scale), pw[tok - key - 1]) : 0.f;
+                store_split2(Ph + (size_t)tok * LDC + key, Pl + (size_t)tok * LDC + key, p0, p1);
+            }
+        }
+        __syncthreads();
+        // ---- o = P v + d^(t + 1) q^T S0 ----
+        float o1[4][4] = {};
+        for (int k0 = 0; k0 < C; k0 += 16) {
+            uint32_t ah[4], al[4];
+            load_a(ah, Ph, LDC, mt * 16, k0, g, t);
+            load_a(al, Pl, LDC, mt * 16, k0, g, t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t b0, b1;
+                load_b(b0, b1, Vt, LDC, half * 32 + j * 8, k0, g, t);
+                mma_bf16(o1[j], ah, b0, b1);
+                mma_bf16(o1[j], al, b0, b1);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int col = c0 + half * 32 + j * 8 + 2 * t;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int tok = mt * 16 + g + hrow * 8;
+                if (tok < nt && col < dv) {
+                    const float f = __fmul_rn(pw[tok + 1], q_scale);
+                    float* dst = o + (size_t)(first + t0 + tok) * row_o + (size_t)h * dv + col;
+                    dst[0] = __fadd_rn(o1[j][2 * hrow], __fmul_rn(f, o2[j][2 * hrow]));
+                    if (col + 1 < dv) dst[1] = __fadd_rn(o1[j][2 * hrow + 1], __fmul_rn(f, o2[j][2 * hrow + 1]));
+                }
+            }
+        }
+        // ---- S = d^n S0 + v^T (weighted k): this warp's 16 value columns and half of the key channels ----
+        const float dn = pw[nt];
+#pragma unroll
+        for (int j = 0; j < NS; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[j][e] = __fmul_rn(sacc[j][e], dn);
+        for (int k0 = 0; k0 < C; k0 += 16) {
+            uint32_t a[4];
+            load_a(a, Vt, LDC, mt * 16, k0, g, t);
+#pragma unroll
+            for (int j = 0; j < NS; ++j) {
+                uint32_t b0, b1;
+                load_b(b0, b1, Kh, LDC, half * (DK / 2) + j * 8, k0, g, t);
+                mma_bf16(sacc[j], a, b0, b1);
+                load_b(b0, b1, Kl, LDC, half * (DK / 2) + j * 8, k0, g, t);
+                mma_bf16(sacc[j], a, b0, b1);
+            }
+        }
+        __syncthreads();       // everyone has read the parked state of the chunk before
+        park_state();
+    }
+#pragma unroll
+    for (int j = 0; j < NS; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int col = c0 + vrow + (e >> 1) * 8, ch = kcol0 + j * 8 + (e & 1);
+            if (col < dv) S[(size_t)ch * dv + col] = sacc[j][e];
+        }
+}
+
+template <int DK>
+constexpr size_t smem_bytes() {
+    return (size_t)(2 * C * (DK + 8) + DVB * LDC + 2 * DK * LDC + 2 * C * LDC + 2 * DVB * (DK + 8)) * sizeof(__nv_bfloat16) +
+           (C + 1) * sizeof(float);
+}
+
+// whether the tensor-core form takes this shape (JLLM_B200_LIGHTNING_TC=0 keeps every shape on the float32 kernels)
+inline bool fits(int dtype, int ld, int q_off, int k_off, int v_off, int dk, int dv, const void* proj) {
+    static const bool on = [] {
+        const char* e = getenv("JLLM_B200_LIGHTNING_TC");
+        return !(e && e[0] == '0');
+    }();
+    return on && dtype == JLLM_BF16 && (dk == 64 || dk == 128) && dv % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
+           k_off % 8 == 0 && v_off % 8 == 0 && ((uintptr_t)proj % 16) == 0;
+}
+
+}  // namespace lightning
+
 }  // namespace
 
 JLLM_BOUNDS_READER(linear_attention)
@@ -649,6 +926,27 @@ JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off,
     JLLM_REQUIRE(dk <= 512 && heads <= 65535 && (dv + 31) / 32 <= 65535 && (max_len + CHUNK - 1) / CHUNK <= 65535,
                  "gla_chunked: dk=%d is above 512, or a segment of %d rows is too long", dk, max_len);
     if (segments == 0 || rows == 0 || max_len == 0) return JLLM_OK;
+    if (head_decay && lightning::fits(dtype, ld, q_off, k_off, v_off, dk, dv, proj)) {
+        // one decay per head, bfloat16 projections, key heads of 64 or 128: the chunks of 64 tokens on the tensor cores
+        if (activation) {
+            const int code = launch_fixed_decay<__nv_bfloat16>((void*)proj, ld, q_off, k_off, v_off, nullptr, head_decay, rows,
+                                                               heads, dk, dv, 1, activation, stream);
+            if (code) return code;
+        }
+        const dim3 grid(segments, heads, (dv + lightning::DVB - 1) / lightning::DVB);
+        if (dk == 64) {
+            const size_t smem = lightning::smem_bytes<64>();
+            cudaFuncSetAttribute(lightning::chunk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            jllm_launch(lightning::chunk_kernel<64>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)proj,
+                        ld, q_off, k_off, v_off, head_decay, state, seg_start, seg_len, state_slots, o, heads, dv, num_slots, q_scale);
+        } else {
+            const size_t smem = lightning::smem_bytes<128>();
+            cudaFuncSetAttribute(lightning::chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            jllm_launch(lightning::chunk_kernel<128>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)proj,
+                        ld, q_off, k_off, v_off, head_decay, state, seg_start, seg_len, state_slots, o, heads, dv, num_slots, q_scale);
+        }
+        return jllm_check_launch("lightning_chunk");
+    }
     if (head_decay) {
         const int code = dtype == JLLM_F32
             ? launch_fixed_decay<float>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 1, activation, stream)
