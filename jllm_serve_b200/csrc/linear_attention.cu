@@ -607,8 +607,8 @@ gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
 // A block owns 64 value columns of one (segment, head): the state's columns do not depend on one another. Eight warps:
 // warp w takes the 16 tokens (w & 3) of the chunk for P and o, with half (w >> 2) of the keys or of the block's value
 // columns, and for the state the 16 value columns (w & 3) with half (w >> 2) of the key channels. Operands lie in shared
-// memory with the contraction index contiguous (rows padded by 16 bytes: a warp's fragment loads hit 32 different
-// banks), so every product is the same "row times row" tile loop.
+// memory with the contraction index contiguous (rows padded by 16 bytes: the eight 16-byte rows of an 8 x 8 matrix hit 32
+// different banks), so every product is the same "row times row" tile loop fed by ldmatrix.
 namespace lightning {
 
 constexpr int C = 64;            // tokens of a chunk
@@ -621,20 +621,23 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// the A fragment (16 rows from `row0`, 16 contraction values from `k0`) of a row-major operand
-__device__ __forceinline__ void load_a(uint32_t (&a)[4], const __nv_bfloat16* m, int ld, int row0, int k0, int g, int t) {
-    const __nv_bfloat16* p = m + (size_t)(row0 + g) * ld + k0 + 2 * t;
-    a[0] = *reinterpret_cast<const uint32_t*>(p);
-    a[1] = *reinterpret_cast<const uint32_t*>(p + 8 * ld);
-    a[2] = *reinterpret_cast<const uint32_t*>(p + 8);
-    a[3] = *reinterpret_cast<const uint32_t*>(p + 8 * ld + 8);
+// Four 8 x 8 matrices of bfloat16 from shared memory into the fragments of a warp (lane l names the 16-byte row l & 7
+// of matrix l >> 3)
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
-// the B fragment (8 output columns from `n0`, 16 contraction values from `k0`) of an operand stored [columns][contraction]
-__device__ __forceinline__ void load_b(uint32_t& b0, uint32_t& b1, const __nv_bfloat16* m, int ld, int n0, int k0, int g, int t) {
-    const __nv_bfloat16* p = m + (size_t)(n0 + g) * ld + k0 + 2 * t;
-    b0 = *reinterpret_cast<const uint32_t*>(p);
-    b1 = *reinterpret_cast<const uint32_t*>(p + 8);
+// the A fragment (16 rows from `row0`, 16 contraction values from `k0`) of a row-major operand
+__device__ __forceinline__ void load_a(uint32_t (&a)[4], const __nv_bfloat16* m, int ld, int row0, int k0, int lane) {
+    ldmatrix4(a, m + (size_t)(row0 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + k0 + (lane >> 4) * 8);
+}
+
+// the B fragments of two neighbouring tiles (8 output columns each, from `n0`; 16 contraction values from `k0`) of an
+// operand stored [columns][contraction]: b[0], b[1] for the first tile, b[2], b[3] for the second
+__device__ __forceinline__ void load_b2(uint32_t (&b)[4], const __nv_bfloat16* m, int ld, int n0, int k0, int lane) {
+    ldmatrix4(b, m + (size_t)(n0 + (lane & 7) + (lane >> 4) * 8) * ld + k0 + ((lane >> 3) & 1) * 8);
 }
 
 // v = hi + lo with hi = bfloat16(v), lo = bfloat16(v - hi)
@@ -763,17 +766,20 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         float o2[4][4] = {};
         for (int k0 = 0; k0 < DK; k0 += 16) {
             uint32_t a[4];
-            load_a(a, Qs, LDQ, mt * 16, k0, g, t);
+            load_a(a, Qs, LDQ, mt * 16, k0, lane);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t b0, b1;
-                load_b(b0, b1, Ks, LDQ, half * 32 + j * 8, k0, g, t);
-                mma_bf16(acc[j], a, b0, b1);
+            for (int j = 0; j < 4; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Ks, LDQ, half * 32 + j * 8, k0, lane);
+                mma_bf16(acc[j], a, b[0], b[1]);
+                mma_bf16(acc[j + 1], a, b[2], b[3]);
                 // ... and q^T S0 for this warp's 16 tokens and 32 value columns (the state as two operands)
-                load_b(b0, b1, Sh, LDQ, half * 32 + j * 8, k0, g, t);
-                mma_bf16(o2[j], a, b0, b1);
-                load_b(b0, b1, Sl, LDQ, half * 32 + j * 8, k0, g, t);
-                mma_bf16(o2[j], a, b0, b1);
+                load_b2(b, Sh, LDQ, half * 32 + j * 8, k0, lane);
+                mma_bf16(o2[j], a, b[0], b[1]);
+                mma_bf16(o2[j + 1], a, b[2], b[3]);
+                load_b2(b, Sl, LDQ, half * 32 + j * 8, k0, lane);
+                mma_bf16(o2[j], a, b[0], b[1]);
+                mma_bf16(o2[j + 1], a, b[2], b[3]);
             }
         }
 #pragma unroll
@@ -792,14 +798,16 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         float o1[4][4] = {};
         for (int k0 = 0; k0 < C; k0 += 16) {
             uint32_t ah[4], al[4];
-            load_a(ah, Ph, LDC, mt * 16, k0, g, t);
-            load_a(al, Pl, LDC, mt * 16, k0, g, t);
+            load_a(ah, Ph, LDC, mt * 16, k0, lane);
+            load_a(al, Pl, LDC, mt * 16, k0, lane);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t b0, b1;
-                load_b(b0, b1, Vt, LDC, half * 32 + j * 8, k0, g, t);
-                mma_bf16(o1[j], ah, b0, b1);
-                mma_bf16(o1[j], al, b0, b1);
+            for (int j = 0; j < 4; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Vt, LDC, half * 32 + j * 8, k0, lane);
+                mma_bf16(o1[j], ah, b[0], b[1]);
+                mma_bf16(o1[j], al, b[0], b[1]);
+                mma_bf16(o1[j + 1], ah, b[2], b[3]);
+                mma_bf16(o1[j + 1], al, b[2], b[3]);
             }
         }
 #pragma unroll
@@ -824,14 +832,16 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
             for (int e = 0; e < 4; ++e) sacc[j][e] = __fmul_rn(sacc[j][e], dn);
         for (int k0 = 0; k0 < C; k0 += 16) {
             uint32_t a[4];
-            load_a(a, Vt, LDC, mt * 16, k0, g, t);
+            load_a(a, Vt, LDC, mt * 16, k0, lane);
 #pragma unroll
-            for (int j = 0; j < NS; ++j) {
-                uint32_t b0, b1;
-                load_b(b0, b1, Kh, LDC, half * (DK / 2) + j * 8, k0, g, t);
-                mma_bf16(sacc[j], a, b0, b1);
-                load_b(b0, b1, Kl, LDC, half * (DK / 2) + j * 8, k0, g, t);
-                mma_bf16(sacc[j], a, b0, b1);
+            for (int j = 0; j < NS; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Kh, LDC, half * (DK / 2) + j * 8, k0, lane);
+                mma_bf16(sacc[j], a, b[0], b[1]);
+                mma_bf16(sacc[j + 1], a, b[2], b[3]);
+                load_b2(b, Kl, LDC, half * (DK / 2) + j * 8, k0, lane);
+                mma_bf16(sacc[j], a, b[0], b[1]);
+                mma_bf16(sacc[j + 1], a, b[2], b[3]);
             }
         }
         __syncthreads();       // everyone has read the parked state of the chunk before

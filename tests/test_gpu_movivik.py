@@ -356,6 +356,47 @@ def test_fixed_decay_recurrence_over_segments_slots_and_portions(heads, dk, dv, 
         close(state[slots[r]], S, torch.float32, f"state of {r}", loose=4 if dtype == torch.bfloat16 else 1)
 
 
+@pytest.mark.parametrize("heads, dk, dv, decays", [(2, 128, 128, (0.97, 0.6)), (3, 64, 64, (0.999, 0.0, 1.0)), (1, 128, 40, (0.9,)),
+                                                   (2, 64, 200, (0.5, 0.99))])
+def test_fixed_decay_chunks_on_the_tensor_cores(heads, dk, dv, decays):
+    """Portions that span several chunks of 64 tokens, end inside one, or are shorter than one, on top of states that
+    earlier portions left; value widths that are no multiple of a block's 64 columns; the float32 kernels (no activation
+    there: the rows are activated once, by the first call) must agree."""
+    o_ = ops()
+    g = torch.Generator().manual_seed(heads * 77 + dv)
+    lengths, slots = {"a": 200 + 64 + 65 + 1, "b": 130, "c": 63 + 2}, {"a": 1, "b": 3, "c": 0}
+    steps = [[("a", 200), ("b", 130)], [("c", 63), ("a", 64)], [("a", 65), ("c", 2)], [("a", 1)]]
+    width = heads * (2 * dk + dv)
+    data = {r: (torch.randn(n, width, generator=g) * 1.2).bfloat16() for r, n in lengths.items()}
+    decay = torch.tensor(decays, dtype=torch.float32, device=DEV)
+    q_off, k_off, v_off = 0, heads * dk, 2 * heads * dk
+    state = torch.full((4, heads, dk, dv), 3.0, device=DEV)
+    for s in slots.values():
+        state[s].zero_()
+    fed, got = {r: 0 for r in lengths}, {r: [] for r in lengths}
+    for step in steps:
+        proj = torch.cat([data[r][fed[r]:fed[r] + n] for r, n in step]).to(DEV)
+        counts = [n for _, n in step]
+        rows = sum(counts)
+        starts = [sum(counts[:i]) for i in range(len(counts))]
+        out = torch.full((rows, heads * dv), float("nan"), device=DEV)
+        o_.gla_chunked(proj, q_off, k_off, v_off, torch.empty(rows, heads * dk, device=DEV), state, i32(starts), i32(counts),
+                       i32([slots[r] for r, _ in step]), out, heads, dk, dv, 0.5, 1.0, max(counts),
+                       torch.empty(rows, heads * dk, device=DEV), torch.empty(rows, heads * dk, device=DEV),
+                       torch.empty(rows, heads * o_.GLA_CHUNK, device=DEV), head_decay=decay, activation=1)
+        for (r, n), s in zip(step, starts):
+            got[r].append(out[s:s + n].cpu())
+            fed[r] += n
+    assert (state[2] == 3).all()
+    for r, n in lengths.items():
+        p = P.silu(data[r].double()).bfloat16().double()
+        S = torch.zeros(heads, dk, dv, dtype=torch.float64)
+        want = plain_fixed_decay(p[:, q_off:k_off].view(n, heads, dk) * 0.5, p[:, k_off:v_off].view(n, heads, dk),
+                                 p[:, v_off:].view(n, heads, dv), [float(d) for d in decay.cpu()], S)
+        close(torch.cat(got[r]), want.view(n, -1), torch.float32, f"outputs of {r}", loose=4)
+        close(state[slots[r]], S, torch.float32, f"state of {r}", loose=4)
+
+
 # ---- whole models through the step function ---------------------------------------------------------------------------
 
 class Checker:
