@@ -604,15 +604,15 @@ gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
 // accumulation in float32. The state itself stays in float32 registers from the first chunk to the last (it is the
 // accumulator of the last product) and is read from and written to its slot once per portion.
 //
-// A block owns 64 value columns of one (segment, head): the state's columns do not depend on one another. Eight warps:
-// warp w takes the 16 tokens (w & 3) of the chunk for P and o, with half (w >> 2) of the keys or of the block's value
-// columns, and for the state the 16 value columns (w & 3) with half (w >> 2) of the key channels. Operands lie in shared
+// A block owns DVB (64 or 32) value columns of one (segment, head): the state's columns do not depend on one another; the
+// narrower blocks are taken when the wider ones would leave SMs without one (every block makes P for itself). Eight
+// warps: warp w takes the 16 tokens (w & 3) of the chunk for P and o, with half (w >> 2) of the keys or of the block's
+// value columns, and for the state 16 of the block's value columns with a half or a quarter of the key channels. Operands lie in shared
 // memory with the contraction index contiguous (rows padded by 16 bytes: the eight 16-byte rows of an 8 x 8 matrix hit 32
 // different banks), so every product is the same "row times row" tile loop fed by ldmatrix.
 namespace lightning {
 
 constexpr int C = 64;            // tokens of a chunk
-constexpr int DVB = 64;          // value columns of a block
 constexpr int LDC = C + 8;       // row length of operands whose contraction runs over the chunk's tokens
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -656,14 +656,17 @@ __device__ __forceinline__ void store_split2(__nv_bfloat16* hi, __nv_bfloat16* l
     *reinterpret_cast<__nv_bfloat162*>(lo) = l2;
 }
 
-template <int DK>
+template <int DK, int DVB>
 __global__ void __launch_bounds__(256)
 chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
              const float* __restrict__ head_decay, float* __restrict__ state, const int* __restrict__ seg_start,
              const int* __restrict__ seg_len, const int* __restrict__ state_slots, float* __restrict__ o, int heads, int dv,
              int num_slots, float q_scale) {
     constexpr int LDQ = DK + 8;          // row length of operands whose contraction runs over the key channels
-    constexpr int NS = DK / 16;          // 8-wide tiles of a warp's half of the key channels
+    constexpr int OT = DVB / 16;         // 8-wide tiles of the value columns a warp takes for o (half of the block's)
+    constexpr int ST = DVB / 16;         // 16-wide tiles of the block's value columns (rows of the transposed state)
+    constexpr int SPARTS = 8 / ST;       // warps that share such a tile, each with a part of the key channels
+    constexpr int NS = DK / SPARTS / 8;  // 8-wide tiles of a warp's part of the key channels
     extern __shared__ __align__(16) unsigned char lightning_smem[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lightning_smem);   // [C][LDQ]     q
     __nv_bfloat16* Ks = Qs + C * LDQ;                                       // [C][LDQ]     k
@@ -679,7 +682,7 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
     pdl_trigger();
     const int seg = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DVB;
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int mt = w & 3, half = w >> 2;
+    const int mt = w & 3, half = w >> 2, smt = w % ST, spart = w / ST;
     const int first = seg_start[seg], n = seg_len[seg], slot = state_slots[seg];
     if (!jllm_in_bounds(slot, num_slots, BOUNDS_SLOT)) return;
     float* S = state + (((size_t)slot * heads + h) * DK) * dv;
@@ -687,9 +690,9 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         const float d = head_decay[h];
         pw[tid] = expf((float)tid * fmaxf(logf(d), -1e30f));      // (a decay of 0: d^0 = 1, every other power 0)
     }
-    // the state, transposed: this thread's values are (value column c0 + mt * 16 + g [+ 8], key channel half * DK / 2 + j * 8 + 2 t [+ 1])
+    // the state, transposed: this thread's values are (value column c0 + smt * 16 + g [+ 8], key channel spart * DK / SPARTS + j * 8 + 2 t [+ 1])
     float sacc[NS][4];
-    const int vrow = mt * 16 + g, kcol0 = half * (DK / 2) + 2 * t;
+    const int vrow = smt * 16 + g, kcol0 = spart * (DK / SPARTS) + 2 * t;
 #pragma unroll
     for (int j = 0; j < NS; ++j)
 #pragma unroll
@@ -763,7 +766,7 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         __syncthreads();
         // ---- P = q k^T for this warp's 16 tokens and 32 keys, times the decay's powers; parked as two operands ----
         float acc[4][4] = {};
-        float o2[4][4] = {};
+        float o2[OT][4] = {};
         for (int k0 = 0; k0 < DK; k0 += 16) {
             uint32_t a[4];
             load_a(a, Qs, LDQ, mt * 16, k0, lane);
@@ -773,11 +776,15 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
                 load_b2(b, Ks, LDQ, half * 32 + j * 8, k0, lane);
                 mma_bf16(acc[j], a, b[0], b[1]);
                 mma_bf16(acc[j + 1], a, b[2], b[3]);
-                // ... and q^T S0 for this warp's 16 tokens and 32 value columns (the state as two operands)
-                load_b2(b, Sh, LDQ, half * 32 + j * 8, k0, lane);
+            }
+            // ... and q^T S0 for this warp's 16 tokens and its half of the block's value columns (the state as two operands)
+#pragma unroll
+            for (int j = 0; j < OT; j += 2) {
+                uint32_t b[4];
+                load_b2(b, Sh, LDQ, half * (DVB / 2) + j * 8, k0, lane);
                 mma_bf16(o2[j], a, b[0], b[1]);
                 mma_bf16(o2[j + 1], a, b[2], b[3]);
-                load_b2(b, Sl, LDQ, half * 32 + j * 8, k0, lane);
+                load_b2(b, Sl, LDQ, half * (DVB / 2) + j * 8, k0, lane);
                 mma_bf16(o2[j], a, b[0], b[1]);
                 mma_bf16(o2[j + 1], a, b[2], b[3]);
             }
@@ -795,15 +802,15 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         }
         __syncthreads();
         // ---- o = P v + d^(t + 1) q^T S0 ----
-        float o1[4][4] = {};
+        float o1[OT][4] = {};
         for (int k0 = 0; k0 < C; k0 += 16) {
             uint32_t ah[4], al[4];
             load_a(ah, Ph, LDC, mt * 16, k0, lane);
             load_a(al, Pl, LDC, mt * 16, k0, lane);
 #pragma unroll
-            for (int j = 0; j < 4; j += 2) {
+            for (int j = 0; j < OT; j += 2) {
                 uint32_t b[4];
-                load_b2(b, Vt, LDC, half * 32 + j * 8, k0, lane);
+                load_b2(b, Vt, LDC, half * (DVB / 2) + j * 8, k0, lane);
                 mma_bf16(o1[j], ah, b[0], b[1]);
                 mma_bf16(o1[j], al, b[0], b[1]);
                 mma_bf16(o1[j + 1], ah, b[2], b[3]);
@@ -811,8 +818,8 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
             }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int col = c0 + half * 32 + j * 8 + 2 * t;
+        for (int j = 0; j < OT; ++j) {
+            const int col = c0 + half * (DVB / 2) + j * 8 + 2 * t;
 #pragma unroll
             for (int hrow = 0; hrow < 2; ++hrow) {
                 const int tok = mt * 16 + g + hrow * 8;
@@ -824,7 +831,7 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
                 }
             }
         }
-        // ---- S = d^n S0 + v^T (weighted k): this warp's 16 value columns and half of the key channels ----
+        // ---- S = d^n S0 + v^T (weighted k): this warp's 16 value columns and its part of the key channels ----
         const float dn = pw[nt];
 #pragma unroll
         for (int j = 0; j < NS; ++j)
@@ -832,14 +839,14 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
             for (int e = 0; e < 4; ++e) sacc[j][e] = __fmul_rn(sacc[j][e], dn);
         for (int k0 = 0; k0 < C; k0 += 16) {
             uint32_t a[4];
-            load_a(a, Vt, LDC, mt * 16, k0, lane);
+            load_a(a, Vt, LDC, smt * 16, k0, lane);
 #pragma unroll
             for (int j = 0; j < NS; j += 2) {
                 uint32_t b[4];
-                load_b2(b, Kh, LDC, half * (DK / 2) + j * 8, k0, lane);
+                load_b2(b, Kh, LDC, spart * (DK / SPARTS) + j * 8, k0, lane);
                 mma_bf16(sacc[j], a, b[0], b[1]);
                 mma_bf16(sacc[j + 1], a, b[2], b[3]);
-                load_b2(b, Kl, LDC, half * (DK / 2) + j * 8, k0, lane);
+                load_b2(b, Kl, LDC, spart * (DK / SPARTS) + j * 8, k0, lane);
                 mma_bf16(sacc[j], a, b[0], b[1]);
                 mma_bf16(sacc[j + 1], a, b[2], b[3]);
             }
@@ -856,7 +863,7 @@ chunk_kernel(const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_of
         }
 }
 
-template <int DK>
+template <int DK, int DVB>
 constexpr size_t smem_bytes() {
     return (size_t)(2 * C * (DK + 8) + DVB * LDC + 2 * DK * LDC + 2 * C * LDC + 2 * DVB * (DK + 8)) * sizeof(__nv_bfloat16) +
            (C + 1) * sizeof(float);
@@ -877,6 +884,14 @@ inline bool fits(int dtype, int ld, int q_off, int k_off, int v_off, int dk, int
 }  // namespace
 
 JLLM_BOUNDS_READER(linear_attention)
+
+// A test's switch: the value columns a block of the tensor-core chunk kernel owns (32 or 64; 0: chosen from the shape).
+static int g_lightning_width = 0;
+JLLM_EXPORT int jllm_lightning_block_width(int width) {
+    JLLM_REQUIRE(width == 0 || width == 32 || width == 64, "lightning_block_width: %d is not 0, 32 or 64", width);
+    g_lightning_width = width;
+    return JLLM_OK;
+}
 
 // proj [rows, ld]: q at column q_off (heads x dk), k at k_off, v at v_off (heads x dv); z [rows, heads x dk] float32:
 // the decay logits, which this call turns into the decays in place; state [num_slots, heads, dk, dv] float32; o [rows,
@@ -943,18 +958,23 @@ JLLM_EXPORT int jllm_gla_chunked(const void* proj, int dtype, int ld, int q_off,
                                                                heads, dk, dv, 1, activation, stream);
             if (code) return code;
         }
-        const dim3 grid(segments, heads, (dv + lightning::DVB - 1) / lightning::DVB);
+        // blocks of 64 value columns, or of 32 where those would leave SMs without a block
+        const int sms = jllm_device_sm_count() > 0 ? jllm_device_sm_count() : 1;
+        const bool narrow = g_lightning_width ? g_lightning_width == 32 : (long long)segments * heads * ((dv + 63) / 64) < sms;
+#define JLLM_LIGHTNING(DK_, DVB_)                                                                                             \
+    do {                                                                                                                      \
+        const size_t smem = lightning::smem_bytes<DK_, DVB_>();                                                               \
+        cudaFuncSetAttribute(lightning::chunk_kernel<DK_, DVB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        jllm_launch(lightning::chunk_kernel<DK_, DVB_>, dim3(segments, heads, (dv + DVB_ - 1) / DVB_), dim3(256), smem, stream, \
+                    LAUNCH_DEPENDENT, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, head_decay, state, seg_start, seg_len, \
+                    state_slots, o, heads, dv, num_slots, q_scale);                                                           \
+    } while (0)
         if (dk == 64) {
-            const size_t smem = lightning::smem_bytes<64>();
-            cudaFuncSetAttribute(lightning::chunk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            jllm_launch(lightning::chunk_kernel<64>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)proj,
-                        ld, q_off, k_off, v_off, head_decay, state, seg_start, seg_len, state_slots, o, heads, dv, num_slots, q_scale);
+            if (narrow) JLLM_LIGHTNING(64, 32); else JLLM_LIGHTNING(64, 64);
         } else {
-            const size_t smem = lightning::smem_bytes<128>();
-            cudaFuncSetAttribute(lightning::chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            jllm_launch(lightning::chunk_kernel<128>, grid, dim3(256), smem, stream, LAUNCH_DEPENDENT, (const __nv_bfloat16*)proj,
-                        ld, q_off, k_off, v_off, head_decay, state, seg_start, seg_len, state_slots, o, heads, dv, num_slots, q_scale);
+            if (narrow) JLLM_LIGHTNING(128, 32); else JLLM_LIGHTNING(128, 64);
         }
+#undef JLLM_LIGHTNING
         return jllm_check_launch("lightning_chunk");
     }
     if (head_decay) {

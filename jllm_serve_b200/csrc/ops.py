@@ -159,6 +159,7 @@ class _Signatures:
     jllm_gla_recurrent = [P, I, I, I, I, I, P, I, P, I, P, P, P, P, I, I, I, I, F, F, P, I, P]
     jllm_gla_chunked = [P, I, I, I, I, I, P, I, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, F, P, I, P]
     jllm_gated_head_norm = [P, P, I, I, P, I, P, I, I, I, F, F, I, P]
+    jllm_lightning_block_width = [I]
     jllm_head_prepare = [P, I, I, I, I, I, P, P, I, I, I, F, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
     jllm_head_gate = [P, I, I, P, I, I, I, I, P]
     jllm_norm_sum = [P, P, P, P, P, I, I, I, F, F, I, P]
@@ -255,6 +256,14 @@ def gla_chunked(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg_l
           seg_start.data_ptr(), seg_len.data_ptr(), state_slots.data_ptr(), out.data_ptr(), seg_start.numel(), int(max_len),
           heads, key_dim, value_dim, float(query_scale), float(temperature), _head_decay(head_decay, heads), int(activation),
           _stream())
+
+
+def lightning_block_width(width: int = 0) -> None:
+    """A test's switch: the value columns a block of the tensor-core chunk kernel of the fixed-decay linear attention owns
+    (32 or 64); 0 (the default): 32 where blocks of 64 would leave SMs without one."""
+    code = library().jllm_lightning_block_width(int(width))
+    if code:
+        raise KernelError(library().jllm_last_error().decode(errors="replace"))
 
 
 def gated_head_norm(o, gate, gain, eps, scale, out, heads, value_dim, gate_kind: str = "silu") -> None:

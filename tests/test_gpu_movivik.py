@@ -358,11 +358,13 @@ def test_fixed_decay_recurrence_over_segments_slots_and_portions(heads, dk, dv, 
 
 @pytest.mark.parametrize("heads, dk, dv, decays", [(2, 128, 128, (0.97, 0.6)), (3, 64, 64, (0.999, 0.0, 1.0)), (1, 128, 40, (0.9,)),
                                                    (2, 64, 200, (0.5, 0.99))])
-def test_fixed_decay_chunks_on_the_tensor_cores(heads, dk, dv, decays):
+@pytest.mark.parametrize("block_width", [32, 64])
+def test_fixed_decay_chunks_on_the_tensor_cores(heads, dk, dv, decays, block_width):
     """Portions that span several chunks of 64 tokens, end inside one, or are shorter than one, on top of states that
     earlier portions left; value widths that are no multiple of a block's 64 columns; the float32 kernels (no activation
     there: the rows are activated once, by the first call) must agree."""
     o_ = ops()
+    o_.lightning_block_width(block_width)
     g = torch.Generator().manual_seed(heads * 77 + dv)
     lengths, slots = {"a": 200 + 64 + 65 + 1, "b": 130, "c": 63 + 2}, {"a": 1, "b": 3, "c": 0}
     steps = [[("a", 200), ("b", 130)], [("c", 63), ("a", 64)], [("a", 65), ("c", 2)], [("a", 1)]]
@@ -387,6 +389,7 @@ def test_fixed_decay_chunks_on_the_tensor_cores(heads, dk, dv, decays):
         for (r, n), s in zip(step, starts):
             got[r].append(out[s:s + n].cpu())
             fed[r] += n
+    o_.lightning_block_width(0)
     assert (state[2] == 3).all()
     for r, n in lengths.items():
         p = P.silu(data[r].double()).bfloat16().double()
