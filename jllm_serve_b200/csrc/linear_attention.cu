@@ -100,7 +100,9 @@ __global__ void __launch_bounds__(1024)
 gla_recurrent_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                      float* __restrict__ state, const int* __restrict__ seg_start, const int* __restrict__ seg_len,
                      const int* __restrict__ state_slots, float* __restrict__ o, int heads, int dk, int dv, float q_scale,
-                     int num_slots) {
+                     int num_slots, const float* __restrict__ head_decay, int activation) {
+    // `head_decay` (else null): one fixed decay per head instead of the table; `activation` 1: q, k and v are taken through
+    // silu as they are fetched (and rounded to the projections' type, as a pass that stored them would have left them)
     constexpr int EPT = TOKENS * R / CB;            // staged values of k (and of q, of d) a thread fetches per round
     extern __shared__ __align__(16) float smem[];
     const int threads = blockDim.x, G = threads / CB;
@@ -132,6 +134,8 @@ gla_recurrent_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, i
     const int vt = tid / CB, vc = tid - vt * CB;    // the one value of v this thread fetches (threads >= TOKENS x CB / 1)
     const int vpt = (TOKENS * CB + threads - 1) / threads;
     float fk[EPT], fq[EPT], fd[EPT], fv[TOKENS];
+    const float fixed = head_decay ? head_decay[h] : 1.f;
+    auto act = [&](float x) { return activation ? to_float(from_float<T>(x / (1.f + expf(-x)))) : x; };
 
     auto fetch = [&](int t0) {      // the round that starts at token t0: from global memory into registers
         const int nt = min(TOKENS, n - t0);
@@ -142,9 +146,9 @@ gla_recurrent_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, i
             fd[u] = 1.f;
             if (st[u] < nt) {
                 const T* p = proj + base * ld + sp[u];
-                fk[u] = to_float(p[k_off]);
-                fq[u] = to_float(p[q_off]);
-                fd[u] = decay[base * ((size_t)heads * dk) + sd[u]];
+                fk[u] = act(to_float(p[k_off]));
+                fq[u] = act(to_float(p[q_off]));
+                fd[u] = head_decay ? fixed : decay[base * ((size_t)heads * dk) + sd[u]];
             }
         }
 #pragma unroll
@@ -152,7 +156,7 @@ gla_recurrent_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, i
             fv[u] = 0.f;
             if (u < vpt) {
                 const int t = vt + u * (threads / CB);
-                if (t < nt && c0 + vc < dv) fv[u] = to_float(proj[(base + t) * ld + v_off + (size_t)h * dv + c0 + vc]);
+                if (t < nt && c0 + vc < dv) fv[u] = act(to_float(proj[(base + t) * ld + v_off + (size_t)h * dv + c0 + vc]));
             }
         }
     };
@@ -249,7 +253,8 @@ gla_recurrent_kernel(const T* __restrict__ proj, int ld, int q_off, int k_off, i
 template <typename T, int R, int CB, bool V4>
 int launch_recurrent(const void* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                      const int* seg_start, const int* seg_len, const int* state_slots, float* o, int segments, int heads,
-                     int dk, int dv, float q_scale, int num_slots, cudaStream_t stream) {
+                     int dk, int dv, float q_scale, int num_slots, const float* head_decay, int activation,
+                     cudaStream_t stream) {
     const int per_warp = 32 / CB;
     const int G = ((dk + R - 1) / R + per_warp - 1) / per_warp * per_warp;       // row groups: whole warps
     const size_t smem = (size_t)(2 * TOKENS * (3 * dk + CB) + TOKENS * G * CB) * sizeof(float);
@@ -259,7 +264,7 @@ int launch_recurrent(const void* proj, int ld, int q_off, int k_off, int v_off, 
         return jllm_fail(JLLM_CUDA_ERROR, "gla_recurrent: %zu bytes of shared memory refused", smem);
     jllm_launch(kernel, dim3(segments, heads, (dv + CB - 1) / CB), dim3(G * CB), smem, stream, LAUNCH_DEPENDENT,
                 (const T*)proj, ld, q_off, k_off, v_off, decay, state, seg_start, seg_len, state_slots, o, heads, dk, dv,
-                q_scale, num_slots);
+                q_scale, num_slots, head_decay, activation);
     return jllm_check_launch("gla_recurrent");
 }
 
@@ -268,13 +273,14 @@ int launch_recurrent(const void* proj, int ld, int q_off, int k_off, int v_off, 
 template <typename T, int R>
 int launch_recurrent_cols(const void* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                           const int* seg_start, const int* seg_len, const int* state_slots, float* o, int segments,
-                          int heads, int dk, int dv, float q_scale, int num_slots, cudaStream_t stream) {
+                          int heads, int dk, int dv, float q_scale, int num_slots, const float* head_decay, int activation,
+                          cudaStream_t stream) {
     const long long sms = max(1, jllm_device_sm_count());
     const long long units = (long long)segments * heads;
     const bool wide = units * ((dv + 31) / 32) >= sms || dv <= 16;
 #define JLLM_GLA_COLS(CB, V4)                                                                                                  \
     return launch_recurrent<T, R, CB, V4>(proj, ld, q_off, k_off, v_off, decay, state, seg_start, seg_len, state_slots, o, \
-                                          segments, heads, dk, dv, q_scale, num_slots, stream)
+                                          segments, heads, dk, dv, q_scale, num_slots, head_decay, activation, stream)
     if (dk % 4 == 0) {
         if (wide) JLLM_GLA_COLS(32, true);
         JLLM_GLA_COLS(16, true);
@@ -905,11 +911,9 @@ JLLM_EXPORT int jllm_gla_recurrent(const void* proj, int dtype, int ld, int q_of
     JLLM_REQUIRE(dk <= 512 && heads <= 65535 && (dv + 7) / 8 <= 65535, "gla_recurrent: dk=%d is above 512", dk);
     if (segments == 0 || rows == 0) return JLLM_OK;
     const float inv_tau = 1.f / tau;
-    if (head_decay) {     // one fixed decay per head: the table is filled (and q, k, v activated) instead
-        const int code = dtype == JLLM_F32
-            ? launch_fixed_decay<float>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 0, activation, stream)
-            : launch_fixed_decay<__nv_bfloat16>((void*)proj, ld, q_off, k_off, v_off, z, head_decay, rows, heads, dk, dv, 0, activation, stream);
-        if (code) return code;
+    if (head_decay) {
+        // one fixed decay per head: the recurrence takes the decays themselves and activates q, k, v as it fetches them (no
+        // table, no pass in front; `proj` is left as it is)
     } else {       // the decay logits become decays, in place
         const size_t total = (size_t)rows * heads * dk;
         const int blocks = (int)min((size_t)65535, (total + 255) / 256);
@@ -919,7 +923,7 @@ JLLM_EXPORT int jllm_gla_recurrent(const void* proj, int dtype, int ld, int q_of
     }
 #define JLLM_GLA(T, R)                                                                                                       \
     return launch_recurrent_cols<T, R>(proj, ld, q_off, k_off, v_off, z, state, seg_start, seg_len, state_slots, o, segments, \
-                                       heads, dk, dv, q_scale, num_slots, stream)
+                                       heads, dk, dv, q_scale, num_slots, head_decay, head_decay ? activation : 0, stream)
     // A step of single tokens is a chain of a few round trips to memory per block, whatever the block's size: many rows a
     // thread make blocks small enough for several to share an SM. A prompt portion waits more than it computes: few rows
     // a thread, so that more threads hide more of the waiting (at most 32 row groups of 32 columns: 1,024 threads).

@@ -218,10 +218,10 @@ def gla_recurrent(proj, q_off, k_off, v_off, decay_logits, state, seg_start, seg
     given columns; decay_logits [rows, heads x key_dim] float32, OVERWRITTEN with the decays (a launch of its own in
     front of the recurrence); state [slots, heads, key_dim, value_dim] float32, read and written in place at
     `state_slots[segment]`; out [rows, heads x value_dim] float32. With `head_decay` (float32 [heads]) every key channel of
-    head h decays by head_decay[h] instead: decay_logits is then scratch that the call fills, and `activation` 1 applies silu
-    to q, k and v in place in `proj` first."""
+    head h decays by head_decay[h] instead: decay_logits is then not touched, and `activation` 1 takes q, k and v through silu
+    as the kernel fetches them (`proj` is left as it is; the chunked form, `gla_chunked`, activates them in place)."""
     global launch_count
-    launch_count += 1
+    launch_count += 0 if head_decay is not None else 1       # (the decays' own launch in front of the recurrence)
     assert decay_logits.dtype == state.dtype == out.dtype == torch.float32 and proj.stride(1) == 1
     assert decay_logits.is_contiguous() and state.is_contiguous() and out.is_contiguous()
     _call("jllm_gla_recurrent", proj.data_ptr(), _DT[proj.dtype], proj.stride(0), q_off, k_off, v_off,

@@ -100,8 +100,17 @@ class DecoderModel:
         ops.embed_rows(batch.token_ids, self.embedding, x)
         for pe in self.position_encodings:
             pe.on_embedding(x, batch)
-        for i, run in enumerate(self.spec.schedule):
-            self.blocks[run.layer].forward(x, batch, self._run_cache(cache, i))
+        schedule, normed = self.spec.schedule, False
+        for i, run in enumerate(schedule):
+            block = self.blocks[run.layer]
+            if getattr(block, "chains_norms", False):
+                # an arrangement whose last launch can also make the next block's normed input is given that block's gain
+                nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+                gain = nxt.mixer_norm.gain if getattr(nxt, "chains_norms", False) and nxt.eps == block.eps else None
+                normed = block.forward(x, batch, self._run_cache(cache, i), normed=normed, next_gain=gain)
+            else:
+                block.forward(x, batch, self._run_cache(cache, i))
+                normed = False
         n = batch.num_wanted
         if logits_out is None:
             logits_out = torch.empty((n, self.vocab), dtype=torch.float32, device=self.rt.device)

@@ -104,8 +104,9 @@ class SandwichNormBlock(PreNormBlock):
 
     The norms behind are RMS norms with gains of their own (`names.mixer_post_norm`, `names.feed_forward_post_norm`). A
     part's result goes into a float32 buffer (the part is told to write instead of add: `overwrite`; one that cannot gets
-    the buffer zeroed), and one kernel norms it, adds it to the stream and, behind the mixer, also makes the feed-forward's
-    normed input (`ops.norm_chain`)."""
+    the buffer zeroed), and one kernel norms it, adds it to the stream and also makes the normed input of the part that
+    follows: the feed-forward's, or the next block's mixer's (`ops.norm_chain`; the model hands a block the next block's
+    gain where both arrange their norms this way)."""
 
     def __init__(self, spec, dim: int, tensors: dict, prefix: str, runtime, position_encodings):
         super().__init__(spec, dim, tensors, prefix, runtime, position_encodings)
@@ -141,10 +142,16 @@ class SandwichNormBlock(PreNormBlock):
             y.zero_()
         return y
 
-    def forward(self, x, batch, cache) -> None:
+    chains_norms = True        # `forward` takes `normed` and `next_gain` and says whether it made the next block's input
+
+    def forward(self, x, batch, cache, normed: bool = False, next_gain=None) -> bool:
+        """`normed`: the shared buffer of normed rows already holds this block's input (the block in front made it with
+        its last launch). `next_gain`: the gain of the norm in front of the block that follows, if that block can take
+        its input the same way (same width and eps): this block's last launch then makes it, and True is returned."""
         rows = x.shape[0]
         xb = self.rt.buffer("normed", self.dim)[:rows]
-        self.mixer_norm.forward(x, xb)
+        if not normed:
+            self.mixer_norm.forward(x, xb)
         branches = getattr(self.mixer, "forward_branches", None)
         if branches is not None:
             # a mixer of mixers hands over its branches' results as they are: their norms and their sum ride in the same
@@ -153,13 +160,16 @@ class SandwichNormBlock(PreNormBlock):
         else:
             a, gain_a, b, gain_b, scale = self._result(self.mixer, rows), None, None, None, 1.0
             self.mixer.forward(xb, a, batch, cache)
+        nxt = xb if next_gain is not None else None
         if self.feed_forward is None:
-            return ops.norm_chain(x, a, self.mixer_post_gain, self.eps, b, gain_a, gain_b, scale)
+            ops.norm_chain(x, a, self.mixer_post_gain, self.eps, b, gain_a, gain_b, scale, next_out=nxt, gain_next=next_gain)
+            return nxt is not None
         # ... and so does the norm in front of the feed-forward
         ops.norm_chain(x, a, self.mixer_post_gain, self.eps, b, gain_a, gain_b, scale, next_out=xb, gain_next=self.ffn_norm.gain)
         y = self._result(self.feed_forward, rows)
         self.feed_forward.forward(xb, y, batch)
-        ops.norm_chain(x, y, self.ffn_post_gain, self.eps)
+        ops.norm_chain(x, y, self.ffn_post_gain, self.eps, next_out=nxt, gain_next=next_gain)
+        return nxt is not None
 
 
 register_block("sandwich_norm", SandwichNormBlock, replace=True)
