@@ -132,7 +132,7 @@ def movivik_shape(width, heads, kv_heads, ff, runs, chunk=1024, vocab=32768):
     mlp = {"kind": "dense", "ff": ff}
     att = {"type": "attention", "mlp": mlp, "mixer": {
         "heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": chunk},
-        "rot": {"base": 10000.0, "dims": 128, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+        "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}}
     decay = [1.0 - 2.0 ** (-2 - 6 * h / max(1, heads - 1)) for h in range(heads)]
     par = {"type": "parallel", "mlp": mlp, "mixer": {
         "left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,

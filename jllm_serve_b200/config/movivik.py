@@ -8,12 +8,13 @@ cache or state of its own: one `LayerSpec` (j's) named by two entries of `Decode
 * `attention`: grouped-query softmax attention with biases on q, k and v, rotary positions on interleaved pairs (2i,
   2i + 1) of the first `rot.dims` values of a head with YaRN-stretched frequencies (`rot.scaling`: factor, original,
   fast, slow; cos and sin times 0.1 ln(factor) + 1), key heads of `dim` and value heads of `vdim` values, the score
-  multiplier `scale`, a chunk mask (`mask.size`: a position sees only the earlier positions of its own chunk, chunks
-  counted from the sequence's first position) and a sigmoid gate per head.
+  multiplier `scale`, a chunk mask (`mask.size`: a position p sees only the earlier positions of its own chunk, p //
+  size) and a sigmoid gate per head.
 * `parallel`: two mixers on the same input. `left`: the same attention without biases, rotating pairs (i, i + dims / 2),
   dividing q and k by their root mean square behind the rotation, fully causal (a `mask` or a `rot.scaling`, if one is
   given, is honoured as above). `right`: linear attention with one fixed `decay` per head, silu on q, k and v, one RMS norm
-  over all heads and a sigmoid gate. The result is half the sum of the two, each first RMS-normed over the model width.
+  over all heads and a sigmoid gate. The mixer's result is the mean of the two branches' results, each after an RMS norm
+  of its own (with a gain) over the model width.
 
 Keys read: `width`, `vocab`, `norm.eps`, `layers[i].type | mixer | mlp | weights_of`; of an attention `heads`, `kv_heads`,
 `dim`, `vdim`, `scale`, `rot.base | dims | scaling`, `mask.size`; of the linear attention `heads`, `dim`, `vdim`, `decay`;

@@ -144,8 +144,8 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
 // Every attention kernel takes one number, `window`, for the span of keys a row at position P sees besides P itself:
 //   0       every earlier key,
 //   w > 0   the last w keys (a sliding window),
-//   -c < 0  the keys of P's own chunk, chunks of c positions counted from position 0 of the sequence (a row never sees
-//           over a chunk's edge, wherever its prompt was cut).
+//   -c < 0  the keys of P's own chunk (position p lies in chunk p / c: a row never sees over a chunk's edge, whatever
+//           portions its prompt is fed in).
 // The first visible key does not decrease with P, which is what the tile kernels' edge tests rely on.
 __host__ __device__ __forceinline__ int jllm_first_key(int P, int window) {
     return window > 0 ? (P + 1 - window > 0 ? P + 1 - window : 0) : (window < 0 ? P - P % (-window) : 0);

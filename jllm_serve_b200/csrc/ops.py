@@ -862,8 +862,8 @@ def _combine_launches(how, n, rows, kv_heads, head_dim) -> int:
 def attention(q, k_cache, v_cache, out, batch, group, heads, kv_heads, head_dim, page_size, window, scale,
               scratch=None, value_dim: int = 0) -> None:
     """Causal attention of every row of the batch over its own request's cached keys and values. `window`: 0 every
-    earlier key, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions (chunks counted from the
-    sequence's first position). `value_dim`: a value head's width where it is not `head_dim`; the tile kernels take heads
+    earlier key, w > 0 the last w keys, -c < 0 the keys of the row's own chunk of c positions (position p lies in chunk
+    p // c). `value_dim`: a value head's width where it is not `head_dim`; the tile kernels take heads
     of one width only, so such a mixer runs on the plain kernel."""
     one_width = value_dim in (0, head_dim) and k_cache.shape[-1] == head_dim
     if one_width and batch.decode_only and attention_decode_fits(q.dtype, heads, kv_heads, head_dim):

@@ -41,7 +41,7 @@ def i32(v):
 
 @pytest.mark.parametrize("heads, kv_heads, dk, dv, dims, pairing, unit, pre", [
     (4, 2, 24, 16, 16, "interleaved", False, False), (3, 3, 16, 24, 8, "half", True, False),
-    (8, 1, 128, 128, 32, "half", True, False), (6, 1, 96, 64, 96, "interleaved", False, False),
+    (4, 2, 128, 128, 48, "half", True, False), (5, 1, 80, 48, 80, "interleaved", False, False),
     (2, 2, 64, 64, 64, "half", False, True), (1, 1, 40, 300, 0, "half", True, True), (5, 1, 272, 8, 2, "interleaved", True, False),
     (3, 1, 256, 256, 64, "half", True, True), (5, 5, 64, 64, 16, "interleaved", True, False), (4, 2, 128, 128, 128, "interleaved", False, True),
     (2, 1, 256, 256, 256, "half", False, False), (7, 1, 64, 64, 48, "half", True, False), (2, 2, 128, 128, 0, "half", True, True)])
@@ -164,7 +164,7 @@ LENS, Q_LENS = [1, 17, 64, 131, 300, 1000, 77, 401], [1, 17, 30, 131, 200, 65, 1
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H, G, dk, dv, page, chunk", [(4, 2, 24, 16, 16, 20), (3, 3, 16, 24, 4, 16), (6, 1, 96, 64, 16, 200),
+@pytest.mark.parametrize("H, G, dk, dv, page, chunk", [(4, 2, 24, 16, 16, 20), (3, 3, 16, 24, 4, 16), (5, 1, 80, 48, 16, 150),
                                                         (2, 1, 128, 128, 8, 70), (20, 1, 16, 16, 16, 33), (2, 2, 32, 8, 16, 0),
                                                         (1, 1, 40, 300, 2, 5000)])
 def test_plain_attention_with_chunks_and_two_head_widths(dtype, H, G, dk, dv, page, chunk):
