@@ -81,7 +81,7 @@ MOVIVIK_F = {"architecture": "Movivik", "width": 50, "vocab": 61, "norm": {"eps"
 MOVIVIK = {"A": MOVIVIK_A, "B": MOVIVIK_B, "C": MOVIVIK_C, "D": MOVIVIK_D, "E": MOVIVIK_E, "F": MOVIVIK_F}
 
 
-def sharpen(tensors: dict, config: dict) -> dict:
+def sharpen(tensors: dict, config: dict, q_gain: float = 4.0) -> dict:
     """Random weights of N(0, 0.02) leave every activation tiny: every attention nearly uniform, the mixers a rounding
     error beside the embedding; a lost key, a chunk edge that is one position off or a stale state would not show. Here
     every matrix is rescaled so that unit inputs give unit outputs (N(0, 1 / fan-in)) and the embedding to N(0, 1); the
@@ -92,11 +92,71 @@ def sharpen(tensors: dict, config: dict) -> dict:
         if name == "embed":
             out[name] = (t.float() * 50.0).to(t.dtype)
         elif t.dim() == 2:
-            gain = 4.0 if name.endswith(".q") else 1.0
+            gain = q_gain if name.endswith(".q") else 1.0
             out[name] = (t.float() * (gain / (0.02 * t.shape[1] ** 0.5))).to(t.dtype)
         elif name.endswith(".b"):
             out[name] = (t.float() * 25.0).to(t.dtype)
     return out
+
+
+def random_movivik(seed: int) -> dict:
+    """A configuration drawn (seeded) from everything the design's keys allow at small sizes: any order of the two kinds
+    of layers, borrowed weights, layers without a feed-forward, head widths from 8 to 128 (equal and unequal for keys and
+    values; the widths the tile kernels take among them), any number of heads and kv heads, rotations of a part or all of
+    a head, with and without scaling and mask on either attention, chunks of 3 to 130 positions, decays from 0.2 to 1."""
+    import random
+    rng = random.Random(seed)
+    widths = [8, 16, 24, 32, 40, 48, 64, 80, 96, 128]
+
+    def attention(left: bool) -> dict:
+        kv = rng.choice([1, 1, 2, 3])
+        heads = kv * rng.choice([1, 2, 3, 4] if kv > 1 else [1, 2, 4, 5, 8, 18])
+        dim = rng.choice(widths)
+        vdim = dim if rng.random() < 0.5 else rng.choice(widths)
+        dims = dim if rng.random() < 0.4 else 2 * rng.randint(1, dim // 2)
+        if rng.random() < 0.5:
+            dims = max(16, dims // 16 * 16) if dim >= 16 else dims
+        scaling = None
+        if rng.random() < (0.3 if left else 0.8):
+            scaling = (rng.choice([1.5, 2.0, 4.0, 16.0]), rng.choice([8, 32, 100]), rng.choice([4.0, 16.0, 32.0]), rng.choice([0.5, 1.0, 2.0]))
+        chunk = rng.choice([3, 16, 31, 64, 100, 130]) if rng.random() < (0.3 if left else 0.85) else None
+        return _att(heads, kv, dim, vdim, round(rng.uniform(0.6, 1.6) / dim ** 0.5, 4), _rot(min(dims, dim), rng.choice([30.0, 1000.0, 10000.0]), scaling), chunk)
+
+    def linear() -> dict:
+        heads = rng.choice([1, 2, 3, 5])
+        return _lin(heads, rng.choice([8, 12, 16, 32, 64, 128]), rng.choice([8, 16, 24, 40, 64, 72, 128]),
+                    [round(rng.uniform(0.2, 1.0), 4) for _ in range(heads)])
+
+    layers = []
+    for i in range(rng.randint(2, 5)):
+        ff = None if rng.random() < 0.2 else rng.choice([8, 24, 40, 64, 100])
+        same = [j for j, l in enumerate(layers) if "weights_of" not in l]
+        if same and rng.random() < 0.3:
+            j = rng.choice(same)
+            layers.append(dict({k: v for k, v in layers[j].items()}, weights_of=j))
+        elif rng.random() < 0.5:
+            layers.append(_attention(attention(False), ff))
+        else:
+            layers.append(_parallel(attention(True), linear(), ff))
+    return {"architecture": "Movivik", "width": rng.choice([24, 40, 64, 72, 128]), "vocab": rng.choice([53, 128, 300]),
+            "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-4])}, "layers": layers}
+
+
+def movivik_folder_of(config: dict, seed: int = 3, sharp: bool = True, q_gain: float = 4.0) -> Path:
+    """A temporary model folder for any configuration (random, by default sharpened weights; `q_gain`: how far the query
+    projections are scaled up beyond unit outputs)."""
+    from jllm_serve_b200.config import parse_config
+    from jllm_serve_b200.config.registry import architecture_entry, model_type_of
+    from jllm_serve_b200.engine.model import model_wants
+    from jllm_serve_b200.weights import random_tensors, write_safetensors
+    wants = model_wants(architecture_entry(model_type_of(config)), parse_config(config))
+    tensors = random_tensors(wants, seed, "cpu", torch.bfloat16)
+    if sharp:
+        tensors = sharpen(tensors, config, q_gain)
+    d = Path(tempfile.mkdtemp(prefix="jllm_movivik_"))
+    (d / "config.json").write_text(json.dumps(config, indent=1))
+    write_safetensors(d / "model.safetensors", tensors, {"format": "pt"})
+    return d
 
 
 @functools.lru_cache(maxsize=None)

@@ -406,9 +406,9 @@ class Checker:
     """Rows against the plain implementation's float64 logits. float32: every row within the tolerance. bfloat16: nearly
     every row (see `finish`); the rms error and the share of equal choices hold over all rows."""
 
-    def __init__(self, folder, sequences, dtype, what):
+    def __init__(self, folder, sequences, dtype, what, slack=1.0):
         self.cfg, self.w = P.load_plain(folder)
-        self.sequences, self.dtype, self.what = sequences, dtype, what
+        self.sequences, self.dtype, self.what, self.slack = sequences, dtype, what, slack
         self.plain, self.errors, self.flips, self.err2, self.ref2, self.scale = {}, [], 0, 0.0, 0.0, 0.0
         self.seen = set()
 
@@ -429,7 +429,7 @@ class Checker:
         for rid, toks in self.sequences.items():
             missing = [p for p in range(len(toks)) if (rid, p) not in self.seen]
             assert not missing, f"{self.what}: no logits for {rid} positions {missing[:5]}"
-        tol = 2 * TOL[self.dtype] * self.scale        # (float32: a hundred-thousandth of the largest logit)
+        tol = 2 * TOL[self.dtype] * self.scale * self.slack       # (float32: a hundred-thousandth of the largest logit)
         worst = max(self.errors)
         over = [e for e in self.errors if e[0] > tol]
         rms = (self.err2 / max(self.ref2, 1e-300)) ** 0.5
@@ -449,9 +449,11 @@ def run_trace(name, dtype, steps, sequences, what, **kw):
     from jllm_serve_b200.engine import ModelRunner, Segment
     args = dict(dtype=dtype, page_size=16, max_tokens=traces.peak_tokens(steps, 16), max_batch_tokens=512, max_requests=4,
                 ctx=1024, poison_freed_pages=True)
+    slack = kw.pop("slack", 1.0)
     args.update(kw)
-    runner = ModelRunner(movivik_folder(name), **args)
-    checker = Checker(movivik_folder(name), sequences, dtype, f"{name} {what}")
+    folder = name if isinstance(name, Path) else movivik_folder(name)
+    runner = ModelRunner(folder, **args)
+    checker = Checker(folder, sequences, dtype, f"{name if not isinstance(name, Path) else ''} {what}", slack)
     fed = {}
     for st in steps:
         segs = [Segment(e["id"], e["tokens"], fed.get(e["id"], 0), e["want"]) for e in st["entries"]]
@@ -525,6 +527,28 @@ def test_a_state_slot_and_pages_that_are_used_again_start_clean():
 def test_more_rows_than_a_batch_holds_run_as_several_batches():
     seqs = sequences_for("C", (300, 77), seed=12)
     run_trace("C", "float32", traces.all_together(seqs, tail=2), seqs, "a step in parts", max_batch_tokens=64)
+
+
+@pytest.mark.parametrize("seed", [7001, 7002, 7003, 7004, 7005, 7006, 7007, 7008, 7009, 7010])
+def test_a_random_configuration_mixed_and_decoded(seed):
+    """Configurations drawn at random: sizes, layer orders, masks and constants in combinations that the fixed test models
+    do not hold; requests mixed in steps with slots and pages used again, and a tail decoded token by token."""
+    import random
+    from tests.movivik_cases import movivik_folder_of, random_movivik
+    cfg = random_movivik(seed)
+    # (the drawn score multipliers reach 1.6 / sqrt(dim): the queries are scaled up less than in the fixed models, so that
+    # the bfloat16 path's rounding of q and k does not drown its comparison; float32 is exact either way)
+    folder = movivik_folder_of(cfg, seed, q_gain=2.0)
+    rng = random.Random(seed)
+    lengths = [rng.randint(1, 30), rng.randint(40, 140), rng.randint(150, 300), rng.randint(2, 70), rng.randint(100, 200)]
+    seqs = {f"r{i}": random_tokens(n, cfg["vocab"], seed + i) for i, n in enumerate(lengths)}
+    shape = "; ".join(f"{l['type']}{'*' if 'weights_of' in l else ''}" for l in cfg["layers"])
+    for dtype in ("float32", "bfloat16"):
+        # (twice the fixed models' tolerance: a drawn model may norm a part's result that nearly cancels, which magnifies
+        # the rounding of that row; a wrong key, edge or state is off by a thousand times more)
+        run_trace(folder, dtype, traces.mixed(seqs, max_live=4, portion=50, prefill_share=0.7), seqs, f"seed {seed} ({shape}) mixed",
+                  slack=2.0)
+        run_trace(folder, dtype, traces.prompt_then_decode(seqs, tail=40), seqs, f"seed {seed} ({shape}) decoded tail", slack=2.0)
 
 
 # ---- generation and the trace program -----------------------------------------------------------------------------------
