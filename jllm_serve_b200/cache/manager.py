@@ -44,7 +44,8 @@ class CacheNeed:
 class PagedKeysValues(CacheNeed):
     kv_heads: int
     head_dim: int
-    window: int = 0                        # 0 = every earlier position, else the last `window`
+    window: int = 0                        # 0 = every earlier position; w > 0 the last w; -c < 0 the row's own chunk of c
+                                           # positions (pages of chunks that have passed are given back, as under a window)
     planes: int = 2                        # 2: keys and values; 1: one row per position that serves as both (a latent
                                            # from which a mixer makes its keys and values)
 
@@ -294,7 +295,7 @@ class CacheManager:
     def commit(self, request: Hashable, length: int) -> List[Tuple[int, int]]:
         """The request now holds `length` positions. Returns the (group, page) pairs given back
         because a window has passed them."""
-        cap = 2 * (self.num_pages if any(g.need.window > 0 for g in self.paged) else 0) * max(1, len(self.paged))
+        cap = 2 * (self.num_pages if any(g.need.window != 0 for g in self.paged) else 0) * max(1, len(self.paged))
         buf = (ctypes.c_int * max(2, cap))()
         count = ctypes.c_int()
         self._check(native.lib().jh_cache_commit(self._ptr, self._h(request), length, buf, cap, ctypes.byref(count)))

@@ -104,7 +104,8 @@ struct Request {
 
 struct Cache {
     int page_size = 1, num_pages = 0;
-    std::vector<int> windows;               // per paged group; 0 = every earlier position
+    std::vector<int> windows;               // per paged group; 0 = every earlier position, w > 0 = the last w, -c < 0 = the
+                                            // row's own chunk of c positions (position p lies in chunk p / c)
     std::vector<Pool> pools;
     Pool slots;
     std::unordered_map<long long, Request> requests;
@@ -112,8 +113,11 @@ struct Cache {
 
     int pages_for(int positions) const { return (positions + page_size - 1) / page_size; }
     int first_needed_page(int g, int length) const {   // pages below hold only positions no later query can see
-        if (windows[g] <= 0) return 0;
-        return std::max(0, length + 1 - windows[g]) / page_size;
+        const int w = windows[g];
+        if (w == 0) return 0;
+        // the next row, at position `length`, sees the last w keys under a window, its own chunk's keys under chunks
+        const int first = w > 0 ? std::max(0, length + 1 - w) : length - length % (-w);
+        return first / page_size;
     }
     Request* find(long long id) {
         auto it = requests.find(id);
@@ -133,7 +137,7 @@ struct Cache {
         if (length >= r.length) return JH_OK;
         const int keep = pages_for(length);
         for (size_t g = 0; g < pools.size(); ++g) {   // first look, then touch: a refused rewind changes nothing
-            if (windows[g] > 0 && first_needed_page((int)g, r.length) > first_needed_page((int)g, length)) {
+            if (windows[g] != 0 && first_needed_page((int)g, r.length) > first_needed_page((int)g, length)) {
                 const auto& table = r.tables[g];
                 for (int i = first_needed_page((int)g, length); i < keep && i < (int)table.size(); ++i)
                     if (table[i] == RELEASED)

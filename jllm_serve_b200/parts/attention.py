@@ -95,9 +95,9 @@ class GqaAttention(Mixer):
 
     @classmethod
     def cache_need(cls, spec):
-        # a cache row holds a key in its first head_dim values and a value in its first value_dim; a chunk mask gives no
-        # pages back early (the pool's books know windows only)
-        return PagedKeysValues(spec.kv_heads, max(spec.head_dim, spec.v_dim), spec.window)
+        # a cache row holds a key in its first head_dim values and a value in its first value_dim; under a chunk mask the
+        # pages of chunks that have passed are given back as under a window (the need's window is then -chunk)
+        return PagedKeysValues(spec.kv_heads, max(spec.head_dim, spec.v_dim), -spec.chunk if spec.chunk else spec.window)
 
     def _tiles_fit(self) -> bool:
         s = self.spec

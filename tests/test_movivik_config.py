@@ -111,16 +111,39 @@ def test_cache_needs_pages_as_wide_as_the_wider_head_and_a_state_beside_them():
         for i, r in enumerate(spec.schedule):
             m = spec.layers[r.layer].mixer
             if m.kind == "gqa_attention":
-                assert needs[i] == PagedKeysValues(m.kv_heads, max(m.head_dim, m.v_dim), 0) and i not in fixed_of_run
+                assert needs[i] == PagedKeysValues(m.kv_heads, max(m.head_dim, m.v_dim), -m.chunk) and i not in fixed_of_run
             else:
                 a, l = m.branches
-                assert needs[i] == (PagedKeysValues(a.kv_heads, max(a.head_dim, a.v_dim), 0),
+                assert needs[i] == (PagedKeysValues(a.kv_heads, max(a.head_dim, a.v_dim), -a.chunk),
                                     FixedState((l.heads, l.key_dim, l.value_dim), "float32"))
                 assert i in paged_of_run and len(fixed_of_run[i]) == 1
     spec = parse_config(MOVIVIK_A)      # the two runs of the borrowed attention layer share a group (one block table)
     needs = [part_class("mixer", spec.layers[r.layer].mixer.kind).cache_need(spec.layers[r.layer].mixer) for r in spec.schedule]
     paged, fixed, _, _ = group_runs(needs)
     assert [g.runs for g in paged] == [[0, 2], [1], [3]] and [g.runs for g in fixed] == [[1], [3]]
+
+
+def test_pages_of_chunks_that_have_passed_are_given_back():
+    """A group under a chunk mask of 20 positions with pages of 8: once a request's next position lies in a new chunk, the
+    pages that hold only earlier chunks go back to the pool (entries -1), like pages that a window has passed; a rewind
+    behind them is refused."""
+    from jllm_serve_b200.cache import CacheManager
+    m = CacheManager([PagedKeysValues(1, 16, -20), PagedKeysValues(1, 16, 0)], 8, 12, 2)
+    m.open("a")
+    m.reserve("a", 0, 19)
+    assert m.commit("a", 19) == [] and m.table("a", 0).count(-1) == 0          # still inside the first chunk
+    m.reserve("a", 19, 1)
+    released = m.commit("a", 20)                                               # the next row opens the chunk [20, 40)
+    assert [g for g, _ in released] == [0, 0] and m.table("a", 0)[:2] == [-1, -1] and m.table("a", 0)[2] >= 0
+    assert m.table("a", 1).count(-1) == 0                                      # the group without a mask keeps everything
+    m.reserve("a", 20, 45)
+    released = m.commit("a", 65)                                               # chunk [60, 80): pages below 56 go
+    assert m.table("a", 0)[:7] == [-1] * 7 and m.table("a", 0)[7] >= 0 and len(released) == 5
+    with pytest.raises(ValueError):
+        m.truncate("a", 30)
+    m.check()
+    m.close("a")
+    assert m.free_pages() == [12, 12]
 
 
 def test_the_first_key_a_row_sees():
